@@ -17,7 +17,7 @@ from typing import Sequence
 
 import torch
 
-from ..parts.base import CacheView, PagedKVNeed, StateNeed
+from ..parts.base import CacheView, PagedKVNeed, StateNeed, pages_of, state_of
 from ..parts.model import CachePlan
 
 
@@ -38,52 +38,53 @@ class CacheStorage:
         self.pages_per_group = tuple(pages_per_group)
         self.num_state_slots = num_state_slots
         self._owned: dict[int, torch.Tensor] = {}
+        self._states: dict[int, torch.Tensor] = {}
         self.views: list[CacheView] = []
         for index, entry in enumerate(plan.entries):
-            need = entry.need
-            if entry.owner == index and isinstance(need, PagedKVNeed) and need.value_size == 0:
+            if entry.owner != index:
+                continue
+            need, state = pages_of(entry.need), state_of(entry.need)
+            if need is not None and need.value_size == 0:
                 # the values are read out of the key rows: keys only
                 pages = self.pages_per_group[entry.group]
                 self._owned[index] = (
                     torch.zeros((pages, need.num_kv_heads, page_size, need.head_size), dtype=dtype, device=device),
                     None,
                 )
-            elif entry.owner == index and isinstance(need, PagedKVNeed) and need.value_size != need.head_size:
+            elif need is not None and need.value_size != need.head_size:
                 # keys and values of different sizes: one tensor each
                 pages = self.pages_per_group[entry.group]
                 self._owned[index] = tuple(
                     torch.zeros((pages, need.num_kv_heads, page_size, size), dtype=dtype, device=device)
                     for size in (need.head_size, need.value_size)
                 )
-            elif entry.owner == index and isinstance(need, PagedKVNeed):
+            elif need is not None:
                 self._owned[index] = torch.zeros(
                     (2, self.pages_per_group[entry.group], need.num_kv_heads, page_size, need.head_size),
                     dtype=dtype,
                     device=device,
                 )
-            elif entry.owner == index and isinstance(need, StateNeed):
+            if state is not None:
                 if num_state_slots <= 0:
                     raise ValueError("the model has per-request state but the engine has no state slots")
-                self._owned[index] = torch.zeros((num_state_slots, *need.shape), dtype=need.dtype, device=device)
+                self._states[index] = torch.zeros((num_state_slots, *state.shape), dtype=state.dtype, device=device)
         for index, entry in enumerate(plan.entries):
-            need = entry.need
-            if isinstance(need, PagedKVNeed):
+            view = CacheView(writes=False)
+            if pages_of(entry.need) is not None:
                 kv = self._owned[entry.owner]
-                self.views.append(
-                    CacheView(group=entry.group, k=kv[0], v=kv[1], writes=entry.owner == index, page_size=page_size)
-                )
-            elif isinstance(need, StateNeed):
-                self.views.append(CacheView(state=self._owned[entry.owner], writes=entry.owner == index))
-            else:
-                self.views.append(CacheView(writes=False))
+                view = CacheView(group=entry.group, k=kv[0], v=kv[1], writes=entry.owner == index, page_size=page_size)
+            if state_of(entry.need) is not None:
+                view.state = self._states[entry.owner]
+                view.writes = entry.owner == index
+            self.views.append(view)
 
     @property
     def state_tensors(self) -> list[torch.Tensor]:
-        return [t for i, t in self._owned.items() if isinstance(self.plan.entries[i].need, StateNeed)]
+        return list(self._states.values())
 
     def bytes(self) -> int:
         total = 0
-        for owned in self._owned.values():
+        for owned in list(self._owned.values()) + list(self._states.values()):
             for t in (owned if isinstance(owned, tuple) else (owned,)):
                 if t is None:
                     continue

@@ -2,6 +2,7 @@
 from .base import ConfigError, ModelConfig
 from .bomipel import BomipelConfig
 from .engine import EngineConfig
+from .kanavik import KanavikConfig
 from .qwen2 import Qwen2Config
 from .registry import (
     config_class_for,
@@ -16,11 +17,13 @@ from .specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
 register_architecture(Qwen2Config)
 register_architecture(TepavikConfig)
 register_architecture(BomipelConfig)
+register_architecture(KanavikConfig)
 
 __all__ = [
     "BomipelConfig",
     "ConfigError",
     "EngineConfig",
+    "KanavikConfig",
     "LayerSpec",
     "ModelConfig",
     "ModelSpec",

@@ -49,9 +49,12 @@ class LayerSpec:
 
     block: str
     parts: Mapping[str, PartSpec]
+    #: constants of the arrangement itself (a residual multiplier, say), for blocks that have some
+    params: Mapping[str, Any] = field(default_factory=dict)
 
     def __post_init__(self) -> None:
         object.__setattr__(self, "parts", _freeze(self.parts))
+        object.__setattr__(self, "params", _freeze(self.params))
 
 
 @dataclass(frozen=True)

@@ -114,17 +114,27 @@ def _fn(symbol: str, argtypes, variant: str = ""):
 
 
 # ---------------------------------------------------------------------------
-def embed(tokens: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, status: torch.Tensor) -> None:
-    """``residual[t] = table[tokens[t]]`` as float; a token outside the table sets the status word."""
+def embed(tokens: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, status: torch.Tensor,
+          positions: Optional[torch.Tensor] = None, position_table: Optional[torch.Tensor] = None) -> None:
+    """``residual[t] = table[tokens[t]]`` as float; a token outside the table sets the status word.
+    With ``position_table [max_positions, hidden]`` (the table's dtype) the row ``position_table[positions[t]]``
+    is added in 32-bit; a position beyond it sets the status word too."""
     vocab, hidden = table.shape
+    max_positions, pos_ptr, table_ptr = 0, 0, 0
+    if position_table is not None:
+        if positions is None or position_table.dtype != table.dtype or position_table.shape[1] != hidden:
+            raise ValueError("a position table needs positions, the embedding's dtype and its width")
+        max_positions = position_table.shape[0]
+        pos_ptr, table_ptr = _opt(positions, "positions", torch.int32), _dev(position_table, "position_table")
     if tokens.dtype != torch.int32 or residual.dtype != torch.float32:
         raise TypeError("embed takes int32 tokens and a float32 residual")
     if residual.shape != (tokens.shape[0], hidden):
         raise ValueError(f"residual is {tuple(residual.shape)}, expected {(tokens.shape[0], hidden)}")
-    fn = _fn("einf_embed", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    fn = _fn("einf_embed", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                            c_int, c_void_p])
     _check(
         fn(_dev(tokens, "tokens"), _dev(table, "table"), _code(table), _dev(residual, "residual"),
-           tokens.shape[0], hidden, vocab, _dev(status, "status"), _stream()),
+           tokens.shape[0], hidden, vocab, _dev(status, "status"), pos_ptr, table_ptr, max_positions, _stream()),
         "embed",
     )
 
@@ -302,6 +312,25 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
         fn(_dev(gate_up, "gate_up"), _code(gate_up), splits, stride, _dev(out, "out"), _code(out), tokens, inter,
            _stream()),
         "silu_mul",
+    )
+
+
+#: activations of a gated feed-forward's gate branch (``silu`` has launches of its own, :func:`silu_mul`)
+GATE_ACTIVATIONS = {"silu": 2, "gelu_tanh": 1}
+
+
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """``out = act(gate_up[:, :I]) * gate_up[:, I:]`` with ``act`` one of :data:`GATE_ACTIVATIONS`;
+    ``gate_up`` may be float32 partial sums ``[splits, tokens, 2 I]`` of a split-K product."""
+    tokens, inter = out.shape
+    splits, stride = _maybe_split(gate_up, tokens, 2 * inter, "gate_up")
+    if kind not in GATE_ACTIVATIONS:
+        raise ValueError(f"unknown gate activation {kind!r}; known: {sorted(GATE_ACTIVATIONS)}")
+    fn = _fn("einf_act_mul", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p])
+    _check(
+        fn(_dev(gate_up, "gate_up"), _code(gate_up), splits, stride, _dev(out, "out"), _code(out), tokens, inter,
+           GATE_ACTIVATIONS[kind], _stream()),
+        "act_mul",
     )
 
 
@@ -816,8 +845,8 @@ def latent_q_store(
 def per_head_project(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
     """``out[t, h] = weight[h] @ x[t, h]`` for every head: ``x`` and ``out`` are ``[tokens, heads, *]`` views
     with unit stride in their last dimension (slices of wider rows are fine), ``weight`` is
-    ``[heads, out, in]``.  bfloat16 goes to the library's batched product, everything else to the FMA
-    kernel head by head."""
+    ``[heads, out, in]``.  bfloat16 goes to the library's batched product (``out`` bfloat16, or float32
+    for a consumer that wants the sums unrounded), everything else to the FMA kernel head by head."""
     tokens, heads, size_in = x.shape
     if weight.shape[0] != heads or weight.shape[2] != size_in or out.shape != (tokens, heads, weight.shape[1]):
         raise ValueError(f"per_head_project: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
@@ -825,6 +854,11 @@ def per_head_project(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -
         if not x.is_cuda:
             raise KernelError("per_head_project operands must be on a CUDA device: there is no CPU path")
         torch.bmm(x.transpose(0, 1), weight.transpose(1, 2), out=out.transpose(0, 1))
+        return
+    if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and out.dtype == torch.float32:
+        if not x.is_cuda:
+            raise KernelError("per_head_project operands must be on a CUDA device: there is no CPU path")
+        torch.bmm(x.transpose(0, 1), weight.transpose(1, 2), out_dtype=torch.float32, out=out.transpose(0, 1))
         return
     for head in range(heads):
         gemm_simt(x[:, head], weight[head], None, out[:, head])
@@ -1002,9 +1036,12 @@ def conv_silu(
     a_log: Optional[torch.Tensor] = None,
     dt_out: Optional[torch.Tensor] = None,
     decay_out: Optional[torch.Tensor] = None,
+    activation: bool = True,
+    input_bias: Optional[torch.Tensor] = None,
 ) -> None:
-    """Causal convolution per channel, bias and SiLU over the tokens of every request, continued
-    from and into the requests' convolution states.
+    """Causal convolution per channel, bias and SiLU (``activation`` false: none) over the tokens of
+    every request, continued from and into the requests' convolution states.  With ``input_bias``
+    (float32 ``[channels]``) the convolution's input is ``x + input_bias`` (the state holds it so).
 
     ``x [tokens, channels]`` (columns of a wider matrix are fine), ``weight [channels, taps]`` with
     the current token's tap last, ``conv_state [slots, taps - 1, channels]`` float32 (a view whose
@@ -1039,8 +1076,11 @@ def conv_silu(
     fn = _fn(
         "einf_conv_silu",
         [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
-         c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+         c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+         c_void_p, c_void_p],
     )
+    if input_bias is not None and (input_bias.dtype != torch.float32 or input_bias.shape != (channels,)):
+        raise ValueError(f"input_bias must be float32 [{channels}]")
     _check(
         fn(x.data_ptr(), _code(x), stride, _dev(weight, "weight"), _opt(bias, "bias", torch.float32),
            conv_state.data_ptr(), conv_state.stride(0), _opt(seq_of_token, "seq_of_token", torch.int32),
@@ -1048,7 +1088,7 @@ def conv_silu(
            state_slots.shape[0], _dev(out, "out"), channels, taps, tokens, dt_ptr,
            _opt(dt_bias, "dt_bias", torch.float32), _opt(a_log, "a_log", torch.float32),
            0 if dt_out is None else dt_out.data_ptr(), 0 if decay_out is None else decay_out.data_ptr(), heads,
-           _stream()),
+           1 if activation else 0, 0 if input_bias is None else input_bias.data_ptr(), _stream()),
         "conv_silu",
     )
 
@@ -1209,6 +1249,247 @@ def gated_norm(
 
 
 #: head sizes the tensor-core attention kernels take (one build per size)
+# ---------------------------------------------------------------------------
+# The residual stream between sublayers
+MAX_SIDE_SIZE = 256
+#: most terms (tensors of pending sublayer output) one launch adds to the stream
+MAX_PENDING_TERMS = 2
+
+
+def _pending_terms(terms, rows: int, width: int) -> list:
+    """Up to two pending outputs, each ``[rows, width]`` or partial sums ``[splits, rows, width]``, as
+    the launchers' (pointer, dtype code, splits, stride) quadruples."""
+    terms = [t for t in (terms or []) if t is not None]
+    if len(terms) > MAX_PENDING_TERMS:
+        raise UnsupportedSize(f"{len(terms)} pending terms: the kernels add up to {MAX_PENDING_TERMS}")
+    out = []
+    for index in range(MAX_PENDING_TERMS):
+        if index < len(terms):
+            t = terms[index]
+            splits, stride = _maybe_split(t, rows, width, "pending") if t.dim() == 3 else (1, 0)
+            if t.dim() == 2 and t.shape != (rows, width):
+                raise ValueError(f"pending is {tuple(t.shape)}, expected {(rows, width)}")
+            out += [_dev(t, "pending"), _code(t), splits, stride]
+        else:
+            out += [0, FLOAT32, 0, 0]
+    return out
+
+
+def norm_conv(
+    pending,
+    pending_scale: float,
+    residual: torch.Tensor,
+    norm_weight: torch.Tensor,
+    eps: float,
+    conv_weight: Optional[torch.Tensor],
+    conv_state: Optional[torch.Tensor],
+    seq_of_token: torch.Tensor,
+    q_start: torch.Tensor,
+    state_slots: torch.Tensor,
+    out: torch.Tensor,
+    single_tokens: bool = False,
+) -> None:
+    """``residual += pending_scale * sum(pending)`` (a list of up to two tensors, each ``[T, H]`` or
+    partial sums ``[S, T, H]``; None or empty: nothing is added), ``h = residual * rsqrt(mean(residual^2)
+    + eps) * norm_weight`` and, with ``conv_weight [H, taps]`` (float32, the current token's tap last),
+    ``out = h + conv(h)``: a causal convolution over the tokens of each request, continued from and
+    into ``conv_state [slots, taps - 1, H]`` (float32, oldest first; a view whose slot stride may be
+    larger; not needed with one tap).  Everything is 32-bit; ``out`` is rounded once.
+    ``single_tokens``: every request brings one token, and one launch does it all."""
+    tokens, hidden = residual.shape
+    if residual.dtype != torch.float32 or norm_weight.dtype != torch.float32 or norm_weight.shape != (hidden,):
+        raise TypeError("the residual stream and norm weights are float32 [.., hidden]")
+    if out.shape != (tokens, hidden):
+        raise ValueError(f"out is {tuple(out.shape)}, expected {(tokens, hidden)}")
+    if hidden > 16384:
+        raise UnsupportedSize(f"norm_conv keeps a row in shared memory; width {hidden} > 16384")
+    taps, state_ptr, state_stride, num_slots, weight_ptr, scratch_ptr = 0, 0, 0, 0, 0, 0
+    scratch = None
+    if conv_weight is not None:
+        taps = conv_weight.shape[1]
+        if conv_weight.shape != (hidden, taps) or conv_weight.dtype != torch.float32 or not conv_weight.is_contiguous():
+            raise ValueError(f"conv weight must be contiguous float32 {(hidden, taps)}")
+        if not 1 <= taps <= MAX_CONV_TAPS:
+            raise UnsupportedSize(f"the convolution kernels take 1 to {MAX_CONV_TAPS} taps, not {taps}")
+        weight_ptr = conv_weight.data_ptr()
+        if taps > 1:
+            if conv_state is None or conv_state.dtype != torch.float32 or conv_state.shape[1:] != (taps - 1, hidden) \
+                    or conv_state.stride(2) != 1 or conv_state.stride(1) != hidden:
+                raise ValueError(f"conv_state must be float32 [slots, {taps - 1}, {hidden}] with contiguous slots")
+            state_ptr, state_stride, num_slots = conv_state.data_ptr(), conv_state.stride(0), conv_state.shape[0]
+            if not single_tokens:
+                scratch = torch.empty((tokens, hidden), dtype=torch.float32, device=residual.device)
+                scratch_ptr = scratch.data_ptr()
+    fn = _fn(
+        "einf_norm_conv",
+        [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_longlong, c_float, c_void_p, c_void_p, c_float,
+         c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+         c_int, c_int, c_int, c_void_p],
+    )
+    _check(
+        fn(*_pending_terms(pending, tokens, hidden), float(pending_scale), _dev(residual, "residual"),
+           _dev(norm_weight, "norm_weight"), float(eps), weight_ptr, taps, state_ptr, state_stride, num_slots,
+           _opt(seq_of_token, "seq_of_token", torch.int32), _opt(q_start, "q_start", torch.int32),
+           _opt(state_slots, "state_slots", torch.int32), state_slots.shape[0], _dev(out, "out"), _code(out),
+           scratch_ptr, tokens, hidden, 1 if single_tokens else 0, _stream()),
+        "norm_conv",
+    )
+
+
+def stream_tail(
+    residual: torch.Tensor,
+    pending,
+    pending_scale: float,
+    token_ids: torch.Tensor,
+    side: Optional[tuple],
+    depth: Optional[tuple],
+) -> None:
+    """The end of a layer in one pass over every row of the stream, in 32-bit:
+    ``x = residual + pending_scale * sum(pending)`` (as in :func:`norm_conv`); with ``side = (table
+    [vocab, n], gate [n, H], proj_t [n, H], norm [H] float32, eps)``: ``g = gelu(gate x) * table[token]``,
+    ``y = proj_t^T g``, ``x += pending_scale * y * rsqrt(mean(y^2) + eps) * norm``; with ``depth =
+    (history [L + 1, T, H] float32, index, weight [index + 2] float32)``: ``history[index + 1] = x`` and
+    ``x = sum_(j <= index + 1) weight[j] history[j]``.  The result replaces ``residual``."""
+    tokens, hidden = residual.shape
+    if residual.dtype != torch.float32:
+        raise TypeError("the residual stream is float32")
+    if hidden > 16384:
+        raise UnsupportedSize(f"stream_tail keeps a row in shared memory; width {hidden} > 16384")
+    side_args = [0, 0, 0, FLOAT32, 0, 0, 0, 0.0]
+    if side is not None:
+        table, gate, proj_t, norm, eps = side
+        size = table.shape[1]
+        if gate.shape != (size, hidden) or proj_t.shape != (size, hidden) or norm.shape != (hidden,) or \
+                norm.dtype != torch.float32 or not (table.dtype == gate.dtype == proj_t.dtype):
+            raise ValueError("side input: table [vocab, n], gate [n, H], proj_t [n, H] of one dtype, norm float32 [H]")
+        if size > MAX_SIDE_SIZE:
+            raise UnsupportedSize(f"a token input of {size} values: the kernel takes up to {MAX_SIDE_SIZE}")
+        side_args = [_dev(table, "table"), _dev(gate, "gate"), _dev(proj_t, "proj_t"), _code(table), _dev(norm, "norm"),
+                     size, table.shape[0], float(eps)]
+    depth_args = [0, 0, 0, 0]
+    if depth is not None:
+        history, index, weight = depth
+        if history.dtype != torch.float32 or history.shape[1:] != (tokens, hidden) or not history.is_contiguous() or \
+                not 0 <= index < history.shape[0] - 1 or weight.shape != (index + 2,) or weight.dtype != torch.float32:
+            raise ValueError("depth average: history float32 [L + 1, T, H], weight float32 [index + 2]")
+        depth_args = [history.data_ptr(), int(index), _dev(weight, "depth weight"), tokens * hidden]
+    fn = _fn(
+        "einf_stream_tail",
+        [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_longlong, c_float, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_longlong,
+         c_int, c_int, c_void_p],
+    )
+    _check(
+        fn(_dev(residual, "residual"), *_pending_terms(pending, tokens, hidden), float(pending_scale),
+           _opt(token_ids, "token_ids", torch.int32), *side_args, *depth_args, tokens, hidden, _stream()),
+        "stream_tail",
+    )
+
+
+# ---------------------------------------------------------------------------
+# Attention whose heads' scores meet before the softmax
+MIXED_MAX_HEADS = 32
+
+
+def paged_attention_mixed(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_of_token: torch.Tensor,
+    positions: torch.Tensor,
+    out: torch.Tensor,
+    scale: float,
+    window: Optional[int],
+    slopes: Optional[torch.Tensor],
+    talk: Optional[torch.Tensor],
+    sink: Optional[torch.Tensor],
+    out_scale: float,
+    status: torch.Tensor,
+) -> None:
+    """Causal (optionally windowed) attention over the paged cache in which all heads of a query are
+    computed together: ``s_h(i, j) = scale q_h(i).k_g(j) - slopes[h] (i - j)``, then ``s_h <- sum_g talk[h,
+    g] s_g`` over all query heads, then a softmax over the visible keys whose denominator also holds
+    ``exp(sink[h])``, then ``out_h = out_scale * sum_j p_h(j) v_g(j)``.  ``slopes``, ``talk`` and ``sink``
+    (float32 ``[H]``, ``[H, H]``, ``[H]``) are each optional.  ``q [T, H, D]``, caches ``[pages, G, page,
+    D]`` and ``[pages, G, page, V]``, ``out [T, H, V]``; scores, weights and sums are 32-bit."""
+    tokens, heads, key_size = q.shape
+    num_pages, kv_heads, page_size, size = k_cache.shape
+    value_size = v_cache.shape[3]
+    if size != key_size or v_cache.shape[:3] != k_cache.shape[:3] or heads % kv_heads:
+        raise ValueError(f"q {tuple(q.shape)}, k_cache {tuple(k_cache.shape)}, v_cache {tuple(v_cache.shape)}")
+    if out.shape != (tokens, heads, value_size) or out.dtype != q.dtype or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise ValueError("out must be [tokens, heads, value_size] and share q's dtype with the caches")
+    if heads > MIXED_MAX_HEADS:
+        raise UnsupportedSize(f"{heads} heads: the score-mixing kernel takes up to {MIXED_MAX_HEADS}")
+    if max(key_size, value_size) > MAX_HEAD_SIZE:
+        raise UnsupportedSize(f"head sizes up to {MAX_HEAD_SIZE}, got {key_size}, {value_size}")
+    for name, t, shape in (("slopes", slopes, (heads,)), ("talk", talk, (heads, heads)), ("sink", sink, (heads,))):
+        if t is not None and (t.dtype != torch.float32 or t.shape != shape):
+            raise ValueError(f"{name} must be float32 {shape}")
+    fn = _fn(
+        "einf_paged_attention_mixed",
+        [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+         c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p],
+    )
+    _check(
+        fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), _code(q),
+           _opt(block_table, "block_table", torch.int32), block_table.shape[1],
+           _opt(seq_of_token, "seq_of_token", torch.int32), _opt(positions, "positions", torch.int32),
+           _dev(out, "out"), tokens, heads, kv_heads, key_size, value_size, page_size, num_pages, float(scale),
+           int(window or 0), _opt(slopes, "slopes", torch.float32), _opt(talk, "talk", torch.float32),
+           _opt(sink, "sink", torch.float32), float(out_scale), _dev(status, "status"), _stream()),
+        "paged_attention_mixed",
+    )
+
+
+def gated_scan(
+    gates: torch.Tensor,
+    gate_bias: torch.Tensor,
+    u: torch.Tensor,
+    y_raw: torch.Tensor,
+    y_bias: torch.Tensor,
+    rate: torch.Tensor,
+    state: torch.Tensor,
+    q_start: torch.Tensor,
+    state_slots: torch.Tensor,
+    out: torch.Tensor,
+    out_scale: float,
+    max_q_len: Optional[int] = None,
+) -> None:
+    """A gated linear recurrence with one state value per channel, over the tokens of every request,
+    continued from and into ``state [slots, width]`` (float32; a view whose slot stride may be larger).
+    ``gates [T, blocks, 2 part]`` float32 holds per block the raw recurrence gates, then the raw input
+    gates (``gate_bias [blocks, 2 part]`` is added); ``r, i = sigmoid(.)``, ``a = exp(rate r)`` with
+    ``rate [width]`` (negative), ``S <- a S + sqrt(1 - a^2) i u``; ``out = out_scale * S * gelu(y_raw +
+    y_bias)``.  ``u [T, width]`` and ``y_raw`` (columns of a wider matrix are fine) share a dtype with
+    ``out``.  All arithmetic is 32-bit."""
+    tokens, blocks, twice = gates.shape
+    width = blocks * (twice // 2)
+    if gates.dtype != torch.float32 or not gates.is_contiguous() or twice % 2:
+        raise ValueError("gates must be contiguous float32 [tokens, blocks, 2 * part]")
+    for name, t in (("gate_bias", gate_bias), ("y_bias", y_bias), ("rate", rate)):
+        if t.dtype != torch.float32 or t.numel() != (2 * width if name == "gate_bias" else width):
+            raise ValueError(f"{name} must be float32 of the layer's width")
+    if u.shape != (tokens, width) or out.shape != (tokens, width) or y_raw.shape != (tokens, width) or \
+            not (u.dtype == out.dtype == y_raw.dtype):
+        raise ValueError("u, y_raw and out are [tokens, width] of one dtype")
+    if state.dtype != torch.float32 or state.shape[1] != width or state.stride(1) != 1:
+        raise ValueError(f"state must be float32 [slots, {width}]")
+    fn = _fn(
+        "einf_gated_scan",
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
+         c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_int, c_void_p],
+    )
+    _check(
+        fn(_dev(gates, "gates"), _dev(gate_bias, "gate_bias"), _dev(u, "u"), y_raw.data_ptr(), _code(u),
+           _rows_of(y_raw, "y_raw"), y_bias.data_ptr(), _dev(rate, "rate"), state.data_ptr(), state.stride(0),
+           state.shape[0], _opt(q_start, "q_start", torch.int32), _opt(state_slots, "state_slots", torch.int32),
+           state_slots.shape[0], _dev(out, "out"), float(out_scale), width, blocks, _stream()),
+        "gated_scan",
+    )
+
+
 FAST_ATTENTION_MAX_HEAD_SIZE = 128
 #: query rows per tile of the prefill attention kernel
 Q_TILE = 128

@@ -44,6 +44,11 @@ LAUNCHERS = {
     "einf_moe_gemm": "routed",
     "einf_moe_combine": "routed",
     "einf_softcap": "pointwise",
+    "einf_act_mul": "pointwise",
+    "einf_norm_conv": "stream",
+    "einf_stream_tail": "stream",
+    "einf_paged_attention_mixed": "attention_mixed",
+    "einf_gated_scan": "recurrence",
     "einf_argmax": "sampling",
     "einf_sample": "sampling",
     "einf_report": "sampling",

@@ -1,5 +1,5 @@
 """Parts of a model and the model assembled from them."""
-from . import attention, block, embedding, latent, mlp, norm, position, recurrent, routed  # noqa: F401  (registers the kinds)
+from . import attention, block, embedding, latent, mlp, norm, parallel, position, recurrent, routed, stream  # noqa: F401  (registers the kinds)
 from .base import (
     CacheView,
     FeedForward,

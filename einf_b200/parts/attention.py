@@ -14,6 +14,14 @@ mask, keys of another layer, values of another size than keys, a window that als
 ``keep_first`` positions of the sequence, a rotation with neighbouring dimensions paired, and
 ``value_mix``: the first such layer of a model ("source") leaves its values of the step in
 ``ctx.extras``, every later one ("blend") caches ``(1 - m) v + m v_source`` with its stored scalar.
+
+A layer may also mix its heads' scores before the softmax.  ``distance_slopes`` (one number per
+head) takes ``slope_h (i - j)`` off the score of query i and key j; ``talking_heads`` then replaces
+the heads' scores by ``sum_g talk[h, g] score_g`` (a stored matrix over all query heads, whatever
+their key/value head); ``sink`` puts ``exp(sink_h)`` of a stored number per head into the softmax's
+denominator, with no key and no value; ``output_scale`` multiplies the mixed values before they are
+rounded for the output projection.  Such a layer runs a kernel of its own, which computes all
+heads of a query together (``ops.paged_attention_mixed``).
 """
 from __future__ import annotations
 
@@ -47,7 +55,16 @@ class PagedAttention(Mixer):
             specs["o_proj.bias"] = TensorSpec((hidden,), "bias")
         if spec.get("value_mix"):
             specs["value_mix"] = TensorSpec((), "fraction")   # stored by the source layer too, unused there
+        if spec.get("talking_heads"):
+            specs["talk"] = TensorSpec((heads, heads), "near_identity")
+        if spec.get("sink"):
+            specs["sink"] = TensorSpec((heads,), "bias")
         return specs
+
+    @staticmethod
+    def _mixes_scores(spec) -> bool:
+        """Whether the heads' scores meet before the softmax (a kernel of its own computes them)."""
+        return bool(spec.get("distance_slopes") or spec.get("talking_heads") or spec.get("sink"))
 
     @staticmethod
     def _is_general(spec) -> bool:
@@ -58,6 +75,7 @@ class PagedAttention(Mixer):
             or (spec.get("value_head_size") or spec["head_size"]) != spec["head_size"]
             or spec.get("keep_first") or spec.get("value_mix")
             or spec["position"].get("layout", "halves") != "halves"
+            or PagedAttention._mixes_scores(spec) or spec.get("output_scale") is not None
         )
 
     @staticmethod
@@ -69,6 +87,8 @@ class PagedAttention(Mixer):
 
     @classmethod
     def kernel_libraries(cls, spec, runtime):
+        if cls._mixes_scores(spec):
+            return ("pointwise", "attention_mixed", "gemm_simt") + cls._product_libraries(runtime)
         if cls._is_general(spec):
             fast = (f"attention_tcgen05:HEAD_SIZE={int(spec['head_size'])}",) \
                 if cls._general_on_tensor_cores(spec, runtime.dtype) else ()
@@ -135,8 +155,27 @@ class PagedAttention(Mixer):
         if self.value_mix not in (None, "source", "blend"):
             raise ValueError(f"value_mix must be source or blend, got {self.value_mix!r}")
         self.mix = runtime.vector(tensors["value_mix"].reshape(1)) if self.value_mix else None
+        self.mixes_scores = self._mixes_scores(spec)
+        self.output_scale = float(spec["output_scale"]) if spec.get("output_scale") is not None else 1.0
+        self.slopes = self.talk = self.sink = None
+        if self.mixes_scores:
+            if self.softcap or self.chunk or self.keep_first or self.shared_kv:
+                raise ValueError("a layer that mixes its heads' scores has no soft cap, chunks, kept positions or shared keys")
+            if self.num_heads > ops.MIXED_MAX_HEADS:
+                raise ops.UnsupportedSize(f"{self.num_heads} heads: the score-mixing kernel takes up to {ops.MIXED_MAX_HEADS}")
+            if spec.get("distance_slopes"):
+                slopes = [float(v) for v in spec["distance_slopes"]]
+                if len(slopes) != self.num_heads:
+                    raise ValueError(f"{len(slopes)} distance slopes for {self.num_heads} heads")
+                self.slopes = torch.tensor(slopes, dtype=torch.float64).to(torch.float32).to(runtime.device)
+            if spec.get("talking_heads"):
+                self.talk = runtime.vector(tensors["talk"])
+            if spec.get("sink"):
+                self.sink = runtime.vector(tensors["sink"])
+        elif self.output_scale != 1.0:
+            raise ValueError("output_scale is applied by the score-mixing kernel only")
         self.fast = not self.general and ops.has_fast_attention(runtime.dtype, self.head_size)
-        self.general_fast = self.general and self._general_on_tensor_cores(spec, runtime.dtype)
+        self.general_fast = self.general and not self.mixes_scores and self._general_on_tensor_cores(spec, runtime.dtype)
 
     def cache_need(self):
         value = self.value_size if self.value_size != self.head_size else None
@@ -191,7 +230,8 @@ class PagedAttention(Mixer):
         return ops.decode_plan(singles, self.num_heads, self.num_kv_heads, self.head_size, page_size, context)
 
     def launch_group(self):
-        return ("attention", self.num_heads, self.num_kv_heads, self.head_size, self.window, self.fast, self.general)
+        return ("attention", self.num_heads, self.num_kv_heads, self.head_size, self.window, self.fast, self.general,
+                self.mixes_scores)
 
     def attend(self, q, ctx: StepContext, cache: CacheView, out) -> None:
         """bfloat16 with a head size up to 128 (a layer with a chunked mask, a soft cap or unit-norm
@@ -199,6 +239,12 @@ class PagedAttention(Mixer):
         requests that bring one token, tiled prefill for the others, side by side in a mixed batch.  Everything else (the 32-bit path,
         larger heads): the generic kernel."""
         table = ctx.block_tables[cache.group]
+        if self.mixes_scores:
+            ops.paged_attention_mixed(
+                q, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, out, self.scale, self.window,
+                self.slopes, self.talk, self.sink, self.output_scale, ctx.status,
+            )
+            return
         if self.fast or (self.general_fast and ops.has_tcgen05_attention(self.head_size, cache.k.shape[2])):
             singles = ctx.single_tokens.shape[0]
             if singles:

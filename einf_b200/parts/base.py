@@ -1,6 +1,6 @@
 """What a part is, and the registries that map a part's kind to its class.
 
-A model is put together from parts of five categories:
+A model is put together from parts of six categories:
 
 ``mixer``
     mixes information between the tokens of a request (attention here).  It
@@ -15,6 +15,10 @@ A model is put together from parts of five categories:
     position encoding; the attention mixer hands it Q, K, V of the step.
 ``block``
     the arrangement of the parts above in one layer.
+``stream``
+    what a block does to the residual stream or to a sublayer's input besides norms: a short
+    convolution over time in front of a sublayer, a per-layer token input, a weighted sum over
+    the results of all layers so far.
 
 plus ``embedding`` and ``head`` at the two ends of the model.  A part gets its
 sizes and constants from its :class:`~einf_b200.config.specs.PartSpec` and its
@@ -32,7 +36,7 @@ import torch
 
 from ..config.specs import PartSpec, TensorSpec
 
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "stream")
 _REGISTRY: dict[str, dict[str, type]] = {category: {} for category in CATEGORIES}
 
 
@@ -108,6 +112,54 @@ class StateNeed:
 
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class PagesAndState:
+    """Both at once: a layer whose mixer attends over pages and also carries a state row (two
+    mixers side by side, or a block that keeps inputs of its own beside its mixer's cache)."""
+
+    pages: PagedKVNeed
+    state: StateNeed
+
+
+def pages_of(need) -> Optional[PagedKVNeed]:
+    """The paged part of a need, or None."""
+    if isinstance(need, PagesAndState):
+        return need.pages
+    return need if isinstance(need, PagedKVNeed) else None
+
+
+def state_of(need) -> Optional[StateNeed]:
+    """The state part of a need, or None."""
+    if isinstance(need, PagesAndState):
+        return need.state
+    return need if isinstance(need, StateNeed) else None
+
+
+def join_needs(*needs):
+    """One need for several (None entries are skipped): at most one of them may want pages; state
+    rows of one dtype are laid end to end, in the order given.  Returns the joined need and, per
+    given need, the offset of its state inside the joined row (None where it has no state)."""
+    pages, floats, dtype, offsets = None, 0, None, []
+    for need in needs:
+        paged, state = pages_of(need), state_of(need)
+        if paged is not None:
+            if pages is not None:
+                raise ValueError("only one of the joined needs may want pages")
+            pages = paged
+        if state is None:
+            offsets.append(None)
+            continue
+        if len(state.shape) != 1 or (dtype is not None and state.dtype != dtype):
+            raise ValueError("joined state needs are flat rows of one dtype")
+        dtype = state.dtype
+        offsets.append(floats)
+        floats += state.shape[0]
+    state = StateNeed((floats,), dtype) if dtype is not None else None
+    if pages is not None and state is not None:
+        return PagesAndState(pages, state), offsets
+    return (pages if pages is not None else state), offsets
 
 
 @dataclass
@@ -217,7 +269,7 @@ class Mixer(Part):
     """``forward`` returns ``[T, hidden]`` in the activation type, or float32 partial sums
     ``[splits, T, hidden]`` that the next norm adds up (what a split-K product leaves)."""
 
-    def cache_need(self) -> PagedKVNeed | StateNeed | None:
+    def cache_need(self) -> "PagedKVNeed | StateNeed | PagesAndState | None":
         return None
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:

@@ -6,6 +6,10 @@ residual stream.  ``linear_head``: ``logits = x @ W^T`` without bias, in 32-bit
 output; with ``tied_to`` it uses that tensor (the embedding table) instead of
 one of its own (``qwen.py:690-696``).  The reference computes logits for every
 token (``qwen.py:772-773``); here only the wanted rows reach the head.
+
+With ``max_positions`` in its spec the embedding also has a learned vector per position,
+``positions [max_positions, hidden]``, added unscaled in the same kernel: ``h0[t] = table[token[t]]
++ positions[position[t]]``; a position beyond the table sets the step's status word.
 """
 from __future__ import annotations
 
@@ -20,7 +24,10 @@ from .base import Part, register_part
 class TokenEmbedding(Part):
     @classmethod
     def tensor_specs(cls, spec):
-        return {"weight": TensorSpec((spec["vocab_size"], spec["hidden_size"]))}
+        specs = {"weight": TensorSpec((spec["vocab_size"], spec["hidden_size"]))}
+        if spec.get("max_positions"):
+            specs["positions"] = TensorSpec((spec["max_positions"], spec["hidden_size"]))
+        return specs
 
     @classmethod
     def kernel_libraries(cls, spec, runtime):
@@ -30,10 +37,14 @@ class TokenEmbedding(Part):
         super().__init__(spec, tensors, runtime)
         self.table = runtime.matrix(tensors["weight"])
         self.hidden_size = int(spec["hidden_size"])
+        self.position_table = runtime.matrix(tensors["positions"]) if spec.get("max_positions") else None
 
     def forward(self, ctx) -> torch.Tensor:
         residual = torch.empty((ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=self.table.device)
-        ops.embed(ctx.token_ids, self.table, residual, ctx.status)
+        if self.position_table is None:
+            ops.embed(ctx.token_ids, self.table, residual, ctx.status)
+        else:
+            ops.embed(ctx.token_ids, self.table, residual, ctx.status, ctx.positions, self.position_table)
         return residual
 
 

@@ -1,4 +1,4 @@
-"""Feed-forwards.  ``gated_mlp``: ``down(act(gate(x)) * up(x))``; ``dense_mlp``: ``down(act(up(x)))``
+"""Feed-forwards.  ``gated_mlp``: ``down(act(gate(x)) * up(x))`` with SiLU or the tanh form of GELU; ``dense_mlp``: ``down(act(up(x)))``
 with the square of ReLU (``relu2``), the tanh form of GELU, SiLU or ReLU.
 
 Gate and up share one matrix product on the concatenated weight, gate rows
@@ -31,8 +31,9 @@ class GatedMLP(FeedForward):
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
-        if spec.get("activation", "silu") != "silu":
-            raise ValueError(f"gated_mlp has a SiLU kernel only, not {spec['activation']!r}")
+        self.activation = str(spec.get("activation", "silu"))
+        if self.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"gated_mlp knows the activations {sorted(ops.GATE_ACTIVATIONS)}, not {self.activation!r}")
         self.hidden_size = int(spec["hidden_size"])
         self.intermediate_size = int(spec["intermediate_size"])
         gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
@@ -46,7 +47,10 @@ class GatedMLP(FeedForward):
         dtype, device = self.runtime.dtype, x.device
         gate_up = ops.project(x, self.gate_up_weight, ctx.status)   # [T, 2I], or split-K partial sums
         hidden = torch.empty((tokens, self.intermediate_size), dtype=dtype, device=device)
-        ops.silu_mul(gate_up, hidden)
+        if self.activation == "silu":
+            ops.silu_mul(gate_up, hidden)
+        else:
+            ops.act_mul(gate_up, hidden, self.activation)
         return ops.project(hidden, self.down_weight, ctx.status)
 
 

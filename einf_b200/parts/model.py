@@ -13,7 +13,8 @@ import torch
 
 from ..config.specs import ModelSpec, PartSpec, TensorSpec
 from .base import (
-    CacheView, PagedKVNeed, Runtime, StateNeed, StepContext, build_part, checkpoint_name, part_class, walk_part_specs,
+    CacheView, PagedKVNeed, PagesAndState, Runtime, StateNeed, StepContext, build_part, checkpoint_name, part_class,
+    pages_of, state_of, walk_part_specs,
 )
 from .block import build_block
 
@@ -24,7 +25,8 @@ def _part_specs(model_spec: ModelSpec):
     for layer in model_spec.layers:
         block_class = part_class("block", layer.block)
         for role, category in block_class.part_categories().items():
-            yield from walk_part_specs(category, layer.parts[role])
+            if role in layer.parts or role not in getattr(block_class, "optional_roles", ()):
+                yield from walk_part_specs(category, layer.parts[role])
     yield from walk_part_specs("norm", model_spec.final_norm)
     yield from walk_part_specs("head", model_spec.head)
 
@@ -53,7 +55,7 @@ def kernel_libraries(model_spec: ModelSpec, runtime: Runtime) -> tuple[str, ...]
 class EntryCache:
     """Cache of one schedule entry: ``owner`` is the entry whose storage it uses."""
 
-    need: PagedKVNeed | StateNeed | None
+    need: PagedKVNeed | StateNeed | PagesAndState | None
     owner: int
     group: int = -1   # page group of a paged need
 
@@ -68,7 +70,7 @@ class CachePlan:
 
     @property
     def has_state(self) -> bool:
-        return any(isinstance(e.need, StateNeed) for e in self.entries)
+        return any(state_of(e.need) is not None for e in self.entries)
 
 
 class DecoderModel:
@@ -95,10 +97,14 @@ class DecoderModel:
         windows: list[tuple[Optional[int], int]] = []
         entries: list[EntryCache] = []
         for index, entry in enumerate(self.schedule):
-            need = self.blocks[entry.layer].mixer.cache_need()
+            block = self.blocks[entry.layer]
+            # a block that keeps something of its own beside its mixer's cache says so itself
+            need = block.cache_need() if hasattr(block, "cache_need") else block.mixer.cache_need()
             owner = index if entry.cache_from is None else entry.cache_from
             if owner != index:
                 owner_need = entries[owner].need
+                if isinstance(need, PagesAndState):
+                    raise ValueError(f"schedule entry {index} carries a state row and cannot read another entry's cache")
                 if type(owner_need) is not type(need) or (
                     isinstance(need, PagedKVNeed)
                     and (need.num_kv_heads, need.head_size, need.value_size)
@@ -108,12 +114,13 @@ class DecoderModel:
                         f"schedule entry {index} cannot read the cache of entry {owner}: {need} vs {owner_need}"
                     )
             group = -1
-            if isinstance(need, PagedKVNeed):
+            paged = pages_of(need)
+            if paged is not None:
                 if owner != index:
                     group = entries[owner].group
                 else:
                     # a group is a window and the first positions it keeps
-                    key = (need.window, need.keep_first if need.window else 0)
+                    key = (paged.window, paged.keep_first if paged.window else 0)
                     if key not in windows:
                         windows.append(key)
                     group = windows.index(key)

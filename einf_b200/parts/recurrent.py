@@ -183,3 +183,92 @@ class Mamba2(_RecurrentMixer):
         out = torch.empty((tokens, inner), dtype=self.runtime.dtype, device=device)
         ops.gated_norm(y, z, self.norm_weight, out, self.norm_groups, self.eps, gate_first=True, gate_kind="silu")
         return ops.project(out, self.out_weight, ctx.status)
+
+
+@register_part("mixer", "gated_linear_recurrence")
+class GatedLinearRecurrence(Mixer):
+    """A recurrent block with a real-gated linear recurrent unit: a state of one float per channel.
+
+    Two branches of ``width`` channels: ``y = gelu(W_y h + b_y)`` and ``u = conv(W_x h + b_x)``, a causal
+    convolution per channel with bias and no activation (its last ``taps - 1`` inputs are state).  u
+    is cut into ``blocks`` equal parts; in part b ``r = sigmoid(A_b u_b + a_b)`` and ``i = sigmoid(I_b
+    u_b + i_b)`` with square matrices.  ``log a = -c r softplus(lam)`` with the constant c
+    (``decay_constant``), ``S <- a S + sqrt(1 - a^2) i u`` from ``S = 0``, output ``W_o (S y)`` times
+    ``output_scale``.  One product for both branches, one batched product for both gates; gates,
+    decays and the state are 32-bit."""
+
+    @classmethod
+    def tensor_specs(cls, spec):
+        hidden, width, blocks, taps = spec["hidden_size"], spec["width"], spec["blocks"], spec["conv_taps"]
+        part = width // blocks
+        return {
+            "y_proj.weight": TensorSpec((width, hidden)),
+            "y_proj.bias": TensorSpec((width,), "bias"),
+            "x_proj.weight": TensorSpec((width, hidden)),
+            "x_proj.bias": TensorSpec((width,), "bias"),
+            "conv.weight": TensorSpec((width, taps), "conv"),
+            "conv.bias": TensorSpec((width,), "bias"),
+            "gate_a.weight": TensorSpec((blocks, part, part)),
+            "gate_a.bias": TensorSpec((blocks, part), "bias"),
+            "gate_i.weight": TensorSpec((blocks, part, part)),
+            "gate_i.bias": TensorSpec((blocks, part), "bias"),
+            "lam": TensorSpec((width,), "rate"),
+            "o_proj.weight": TensorSpec((hidden, width)),
+        }
+
+    @classmethod
+    def kernel_libraries(cls, spec, runtime):
+        return ("pointwise", "recurrence", "gemm_simt") + (("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ())
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.width, self.blocks, self.taps = int(spec["width"]), int(spec["blocks"]), int(spec["conv_taps"])
+        if self.width % self.blocks:
+            raise ValueError(f"a width of {self.width} is not a multiple of {self.blocks} blocks")
+        if not 1 <= self.taps <= ops.MAX_CONV_TAPS:
+            raise ops.UnsupportedSize(f"{self.taps} taps: the convolution kernel takes 1 to {ops.MAX_CONV_TAPS}")
+        self.part = self.width // self.blocks
+        self.output_scale = float(spec.get("output_scale", 1.0))
+        matrices = [tensors["y_proj.weight"], tensors["x_proj.weight"]]
+        if len({m.dtype for m in matrices}) > 1:
+            matrices = [m.to(torch.float32) for m in matrices]
+        self.in_weight = runtime.matrix(torch.cat(matrices, dim=0))
+        self.in_bias = runtime.vector(torch.cat([tensors["y_proj.bias"].float(), tensors["x_proj.bias"].float()]))
+        self.conv_weight = runtime.vector(tensors["conv.weight"])
+        self.conv_bias = runtime.vector(tensors["conv.bias"])
+        gates = [tensors["gate_a.weight"], tensors["gate_i.weight"]]
+        if len({m.dtype for m in gates}) > 1:
+            gates = [m.to(torch.float32) for m in gates]
+        # per block the rows of the recurrence gate, then those of the input gate
+        self.gate_weight = runtime.matrix(torch.cat(gates, dim=1))                       # [blocks, 2 part, part]
+        self.gate_bias = runtime.vector(torch.cat([tensors["gate_a.bias"].float(), tensors["gate_i.bias"].float()], dim=1))
+        # log a = rate * r with rate = -c softplus(lam), made once in 64-bit
+        rate = -float(spec["decay_constant"]) * torch.nn.functional.softplus(tensors["lam"].to(torch.float64))
+        self.rate = runtime.vector(rate)
+        self.out_weight = runtime.matrix(tensors["o_proj.weight"])
+
+    def cache_need(self):
+        # the recurrent state, then the convolution's last taps-1 inputs [taps-1, width]
+        return StateNeed((self.width * self.taps,), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        if cache.state is None or not cache.writes:
+            raise ValueError("a gated linear recurrence needs a state of its own")
+        tokens, width, device = x.shape[0], self.width, x.device
+        proj = ops.project(x, self.in_weight, ctx.status, allow_partial=False)           # [T, y | x], bias not yet added
+        state = cache.state
+        recurrent = state[:, :width]
+        conv_state = state[:, width:width * self.taps].unflatten(1, (self.taps - 1, width))
+        u = torch.empty((tokens, width), dtype=proj.dtype, device=device)
+        ops.conv_silu(
+            proj[:, width:], self.conv_weight, self.conv_bias, conv_state, ctx.seq_of_token, ctx.q_start,
+            ctx.state_slots, u, activation=False, input_bias=self.in_bias[width:],
+        )
+        gates = torch.empty((tokens, self.blocks, 2 * self.part), dtype=torch.float32, device=device)
+        ops.per_head_project(u.view(tokens, self.blocks, self.part), self.gate_weight, gates)
+        out = torch.empty((tokens, width), dtype=self.runtime.dtype, device=device)
+        ops.gated_scan(
+            gates, self.gate_bias, u, proj[:, :width], self.in_bias[:width], self.rate, recurrent, ctx.q_start,
+            ctx.state_slots, out, self.output_scale, max_q_len=ctx.max_q_len,
+        )
+        return ops.project(out, self.out_weight, ctx.status)

@@ -5,7 +5,8 @@ initialisation under ``torch.manual_seed``, ``tests/test_torch_qwen.py:72-75``).
 Matrices and biases are drawn N(0, ``init_std``), norm weights
 1 + N(0, ``init_scale_std``) (around zero for a norm that adds the one itself;
 convolution taps, step-size biases and rate logarithms of a state-space layer
-in the ranges such layers are initialised to), one tensor after another in sorted name order
+in the ranges such layers are initialised to; a matrix that mixes heads near the identity;
+weights over the depth near "the newest result"), one tensor after another in sorted name order
 from one seeded CPU generator, and stored in bfloat16, so every reader of the
 folder sees the same values.
 """
@@ -57,6 +58,13 @@ def random_tensors(
             values = torch.sigmoid(values)
         elif spec.role == "a_log":         # the logarithm of a rate between 1 and 16
             values = torch.log(1.0 + 15.0 * torch.sigmoid(values))
+        elif spec.role == "rate":          # softplus of it lies between 0.005 and 0.7: decays from slow to fast
+            values = 1.5 * values - 2.5
+        elif spec.role == "near_identity":  # a square matrix that mixes its rows a little
+            values = torch.eye(spec.shape[-1], device=device) + 0.2 * values
+        elif spec.role == "depth":         # weights over the depth: mostly the newest result
+            values = 0.2 * values / spec.shape[-1]
+            values[..., -1] += 1.0
         else:
             values = std * values
         tensors[name] = values.to(dtype)

@@ -18,8 +18,10 @@ import torch
 _MASK64 = (1 << 64) - 1
 
 
-def embed(tokens, table, residual, status):
+def embed(tokens, table, residual, status, positions=None, position_table=None):
     residual.copy_(table[tokens.long()].float())
+    if position_table is not None:
+        residual.add_(position_table[positions.long()].float())
 
 
 def add_rmsnorm(x, residual, weight, eps, out, rows=None, status=None):
@@ -288,9 +290,11 @@ def softcap(values, cap):
 
 
 def conv_silu(x, weight, bias, conv_state, seq_of_token, q_start, state_slots, out, dt_raw=None, dt_bias=None,
-              a_log=None, dt_out=None, decay_out=None):
+              a_log=None, dt_out=None, decay_out=None, activation=True, input_bias=None):
     taps = weight.shape[1]
     xf = x.float()
+    if input_bias is not None:
+        xf = xf + input_bias
     for r in range(state_slots.shape[0]):
         first, last = int(q_start[r]), int(q_start[r + 1])
         slot = int(state_slots[r])
@@ -302,7 +306,7 @@ def conv_silu(x, weight, bias, conv_state, seq_of_token, q_start, state_slots, o
             acc = (line[i:i + taps].T * weight).sum(dim=1)
             if bias is not None:
                 acc = acc + bias
-            out[first + i] = (acc / (1 + torch.exp(-acc))).to(out.dtype)
+            out[first + i] = ((acc / (1 + torch.exp(-acc))) if activation else acc).to(out.dtype)
         if slot >= 0 and taps > 1:
             conv_state[slot] = line[-(taps - 1):]
     if dt_raw is not None:
@@ -351,6 +355,106 @@ def gated_norm(y, gate, weight, out, parts, eps, gate_first, gate_kind):
     if not gate_first:
         result = result * g
     out.copy_(result.to(out.dtype))
+
+
+def _gelu_tanh(z):
+    return 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+
+
+def act_mul(gate_up, out, kind):
+    g = _summed(gate_up)
+    inter = out.shape[1]
+    gate, up = g[:, :inter], g[:, inter:]
+    act = {"silu": lambda z: z / (1 + torch.exp(-z)), "gelu_tanh": _gelu_tanh}[kind]
+    out.copy_((act(gate) * up).to(out.dtype))
+
+
+def _add_pending(residual, pending, scale):
+    terms = [t for t in (pending or []) if t is not None]
+    if terms:
+        total = _summed(terms[0])
+        for t in terms[1:]:
+            total = total + _summed(t)
+        residual.add_(scale * total)
+
+
+def norm_conv(pending, pending_scale, residual, norm_weight, eps, conv_weight, conv_state, seq_of_token, q_start,
+              state_slots, out, single_tokens=False):
+    _add_pending(residual, pending, pending_scale)
+    h = residual * torch.rsqrt(residual.pow(2).mean(-1, keepdim=True) + eps) * norm_weight
+    if conv_weight is None:
+        out.copy_(h.to(out.dtype))
+        return
+    taps = conv_weight.shape[1]
+    for r in range(state_slots.shape[0]):
+        first, last = int(q_start[r]), int(q_start[r + 1])
+        slot = int(state_slots[r])
+        if last <= first:
+            continue
+        history = conv_state[slot].clone() if (slot >= 0 and taps > 1) else torch.zeros(taps - 1, h.shape[1])
+        line = torch.cat([history, h[first:last]], dim=0)
+        for i in range(last - first):
+            out[first + i] = (h[first + i] + (line[i:i + taps].T * conv_weight).sum(dim=1)).to(out.dtype)
+        if slot >= 0 and taps > 1:
+            conv_state[slot] = line[-(taps - 1):]
+
+
+def stream_tail(residual, pending, pending_scale, token_ids, side, depth):
+    _add_pending(residual, pending, pending_scale)
+    if side is not None:
+        table, gate, proj_t, norm, eps = side
+        g = _gelu_tanh(residual @ gate.float().T) * table[token_ids.long()].float()
+        y = g @ proj_t.float()
+        residual.add_(pending_scale * y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * norm)
+    if depth is not None:
+        history, index, weight = depth
+        history[index + 1] = residual
+        residual.copy_((weight[:, None, None] * history[:index + 2]).sum(0))
+
+
+def paged_attention_mixed(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, slopes, talk,
+                          sink, out_scale, status):
+    tokens, num_heads, _ = q.shape
+    _, num_kv_heads, page_size, _ = k_cache.shape
+    groups = num_heads // num_kv_heads
+    for t in range(tokens):
+        r = int(seq_of_token[t])
+        pos = int(positions[t])
+        lo = max(0, pos - window + 1) if window else 0
+        keys = torch.arange(lo, pos + 1)
+        pages = block_table[r, (keys // page_size).long()].long()
+        offsets = (keys % page_size).long()
+        k = k_cache[pages, :, offsets, :].float().repeat_interleave(groups, dim=1)
+        v = v_cache[pages, :, offsets, :].float().repeat_interleave(groups, dim=1)
+        scores = torch.einsum("hd,nhd->hn", q[t].float(), k) * scale
+        if slopes is not None:
+            scores = scores - slopes[:, None] * (pos - keys).float()[None, :]
+        if talk is not None:
+            scores = talk @ scores
+        if sink is not None:
+            scores = torch.cat([scores, sink[:, None]], dim=1)
+        probabilities = torch.softmax(scores, dim=-1)[:, :keys.shape[0]]
+        out[t] = (out_scale * torch.einsum("hn,nhd->hd", probabilities, v)).to(out.dtype)
+
+
+def gated_scan(gates, gate_bias, u, y_raw, y_bias, rate, state, q_start, state_slots, out, out_scale, max_q_len=None):
+    tokens, blocks, twice = gates.shape
+    part = twice // 2
+    raw = gates + gate_bias.view(1, blocks, twice)
+    r = torch.sigmoid(raw[:, :, :part]).reshape(tokens, -1)
+    i = torch.sigmoid(raw[:, :, part:]).reshape(tokens, -1)
+    a = torch.exp(rate * r)
+    b = torch.sqrt(1.0 - a * a) * i * u.float()
+    y = _gelu_tanh(y_raw.float() + y_bias)
+    for request in range(state_slots.shape[0]):
+        first, last = int(q_start[request]), int(q_start[request + 1])
+        slot = int(state_slots[request])
+        s = state[slot].clone() if slot >= 0 else torch.zeros(u.shape[1])
+        for t in range(first, last):
+            s = a[t] * s + b[t]
+            out[t] = (out_scale * s * y[t]).to(out.dtype)
+        if slot >= 0 and last > first:
+            state[slot] = s
 
 
 def argmax(logits, tokens):
@@ -447,6 +551,7 @@ _NAMES = (
     "zero_fresh_state", "has_fast_attention", "activation", "qkv_norm_store", "conv_silu", "linear_recurrence",
     "gated_norm", "recurrence_plan", "latent_down_store", "latent_q_store", "per_head_project", "router_topk",
     "moe_dispatch", "moe_gemm", "moe_combine", "softcap", "latent_decode_attention", "latent_decode_splits", "moe_gemm_on_tensor_cores", "moe_gemm_splits",
+    "act_mul", "norm_conv", "stream_tail", "paged_attention_mixed", "gated_scan",
 )
 
 
