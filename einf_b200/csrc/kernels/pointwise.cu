@@ -12,23 +12,33 @@ namespace einf {
 
 // ---------------------------------------------------------------------------
 // Embedding: residual[t, :] = table[token[t], :]   (reference: nn.Embedding,
-// src/einf/executors/torch/qwen.py:744)
+// src/einf/executors/torch/qwen.py:744).  With a table of learned position vectors
+// (pos_table [max_positions, hidden]) the row of the token's position is added, unscaled, in
+// 32-bit; a position outside the table sets the same status bit as a bad token.
 // ---------------------------------------------------------------------------
 template <typename TTable>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TTable* __restrict__ table,
-                             float* __restrict__ residual, int hidden, int vocab, int* status) {
+                             float* __restrict__ residual, int hidden, int vocab, int* status,
+                             const int* __restrict__ positions, const TTable* __restrict__ pos_table,
+                             int max_positions) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const int token = tokens[t];
+  const int position = pos_table ? positions[t] : 0;
   float* out = residual + (size_t)t * hidden;
-  if (token < 0 || token >= vocab) {
+  if (token < 0 || token >= vocab || (pos_table && (position < 0 || position >= max_positions))) {
     if (threadIdx.x == 0) atomicOr(status, kStatusBadToken);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = 0.f;
     return;
   }
   const TTable* row = table + (size_t)token * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]);
+  if (pos_table) {
+    const TTable* pos = pos_table + (size_t)position * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]) + to_float(pos[i]);
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]);
+  }
 }
 
 // The input of a consumer may be the partial sums of a split-K product, [splits, T, width].
@@ -801,6 +811,62 @@ __global__ void activation_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __
 }
 
 // ---------------------------------------------------------------------------
+// out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i] for the activations above: the gated
+// feed-forward with another gate than SiLU.  The dense bfloat16 form computes the GELU's tanh as
+// 1 - 2 / (exp(2 a) + 1) with the hardware exponential and reciprocal (the result is rounded to
+// bfloat16); the generic form, which the 32-bit path uses, calls tanhf.
+// ---------------------------------------------------------------------------
+template <typename TIn, typename T>
+__global__ void act_mul_kernel(const TIn* __restrict__ gate_up, int splits, size_t split_stride, T* __restrict__ out,
+                               int intermediate, int kind, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    const size_t t = idx / intermediate;
+    const int i = (int)(idx - t * intermediate);
+    const float g = sum_splits(gate_up + t * 2 * intermediate + i, splits, split_stride);
+    const float u = sum_splits(gate_up + t * 2 * intermediate + intermediate + i, splits, split_stride);
+    out[idx] = from_float<T>(activate(g, kind) * u);
+  }
+}
+
+__device__ __forceinline__ float activate_fast(float z, int kind) {
+  if (kind == 1) {
+    const float a = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    const float th = 1.f - __fdividef(2.f, __expf(2.f * a) + 1.f);
+    return 0.5f * z * (1.f + th);
+  }
+  if (kind == 2) return __fdividef(z, 1.f + __expf(-z));
+  return activate(z, kind);
+}
+
+__global__ void act_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
+                                      int intermediate, int chunks_per_row, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const unsigned t = blockIdx.x / (unsigned)chunks_per_row;
+  const unsigned chunk = blockIdx.x - t * (unsigned)chunks_per_row;
+  const int i = (int)(chunk * blockDim.x + threadIdx.x) << 3;
+  if (i < intermediate) {
+    const __nv_bfloat16* row = gate_up + (size_t)t * 2 * intermediate;
+    const uint4 g = *reinterpret_cast<const uint4*>(row + i);
+    const uint4 u = *reinterpret_cast<const uint4*>(row + intermediate + i);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 result;
+    __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&result);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 gf = __bfloat1622float2(gp[e]);
+      const float2 uf = __bfloat1622float2(up[e]);
+      rp[e] = __floats2bfloat162_rn(activate_fast(gf.x, kind) * uf.x, activate_fast(gf.y, kind) * uf.y);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * intermediate + i) = result;
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Bias, unit-RMS queries and keys, and the cache write of an attention layer without a rotation.
 // One warp per (token, head): the row of the product is [H query heads of `key_size` | G key heads
 // of `key_size` | G value heads of `value_size`] (G = 0: a layer that reads another layer's keys and
@@ -952,12 +1018,13 @@ static inline int pick_threads(int work) {
 }
 
 extern "C" int einf_embed(const int* tokens, const void* table, int table_dtype, float* residual,
-                          int num_tokens, int hidden, int vocab, int* status, cudaStream_t stream) {
+                          int num_tokens, int hidden, int vocab, int* status, const int* positions,
+                          const void* pos_table, int max_positions, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   const int threads = pick_threads(hidden);
   EINF_DISPATCH_2(table_dtype, T, {
     return (int)launch_pdl(embed_kernel<T>, num_tokens, threads, 0, stream, tokens, (const T*)table, residual, hidden,
-                           vocab, status);
+                           vocab, status, positions, (const T*)pos_table, max_positions);
   })
 }
 
@@ -1152,6 +1219,29 @@ extern "C" int einf_silu_mul(const void* gate_up, int in_dtype, int splits, long
     EINF_DISPATCH_2(dtype, T, {
       return (int)launch_pdl(silu_mul_kernel<TIn, T>, (int)blocks, threads, 0, stream, (const TIn*)gate_up, splits,
                              (size_t)split_stride, (T*)out, intermediate, total);
+    })
+  })
+}
+
+extern "C" int einf_act_mul(const void* gate_up, int in_dtype, int splits, long long split_stride, void* out,
+                            int dtype, long long num_tokens, int intermediate, int kind, cudaStream_t stream) {
+  const size_t total = (size_t)num_tokens * intermediate;
+  if (total == 0) return 0;
+  const int threads = 256;
+  if (splits == 1 && in_dtype == kBFloat16 && dtype == kBFloat16 && intermediate % 8 == 0 &&
+      ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const int vectors_per_row = intermediate >> 3;
+    const int chunks = (vectors_per_row + threads - 1) / threads;
+    if ((long long)chunks * num_tokens < (1ll << 31))
+      return (int)launch_pdl(act_mul_bf16x8_kernel, (int)(chunks * num_tokens), threads, 0, stream,
+                             (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, intermediate, chunks, kind);
+  }
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  EINF_DISPATCH_2(in_dtype, TIn, {
+    EINF_DISPATCH_2(dtype, T, {
+      return (int)launch_pdl(act_mul_kernel<TIn, T>, (int)blocks, threads, 0, stream, (const TIn*)gate_up, splits,
+                             (size_t)split_stride, (T*)out, intermediate, kind, total);
     })
   })
 }

@@ -19,7 +19,9 @@ __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + lo
 // Causal convolution per channel over the tokens of each request, bias, SiLU:
 //   out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps - 1) + j, c]),  j = 0 .. taps-1,
 // where inputs before the portion come from the request's convolution state (its last taps-1
-// inputs, oldest first, [taps-1, channels] floats; zeros after a fresh start).  The same launch
+// inputs, oldest first, [taps-1, channels] floats; zeros after a fresh start).  `act` 0 leaves the
+// SiLU out; with `input_bias` the convolution's input is in + input_bias[c] (a projection's bias
+// that is added here instead of by a launch of its own; the state holds the sum).  The same launch
 // turns the raw step sizes of `heads` further columns into
 //   dt = softplus(raw + dt_bias[h])   and   decay = exp(-exp(a_log[h]) * dt)
 // in 32-bit (columns channels .. channels+heads of the work; `in` holds them at dt_offset).
@@ -32,7 +34,8 @@ __global__ void conv_silu_kernel(const T* __restrict__ in, long long in_stride, 
                                  T* __restrict__ out, int channels, int taps, int num_tokens,
                                  const T* __restrict__ dt_in, const float* __restrict__ dt_bias,
                                  const float* __restrict__ a_log, float* __restrict__ dt_out,
-                                 float* __restrict__ decay_out, int heads) {
+                                 float* __restrict__ decay_out, int heads, int act,
+                                 const float* __restrict__ input_bias) {
   pdl_launch_dependents();
   pdl_wait();
   const int columns = channels + heads;
@@ -56,11 +59,11 @@ __global__ void conv_silu_kernel(const T* __restrict__ in, long long in_stride, 
     for (int j = 0; j < taps; ++j) {
       const int u = t - (taps - 1) + j;       // packed index of the input, if it is in this step
       float v;
-      if (u >= first) v = to_float(in[(long long)u * in_stride + c]);
+      if (u >= first) v = to_float(in[(long long)u * in_stride + c]) + (input_bias ? input_bias[c] : 0.f);
       else v = state ? state[(long long)(taps - 1 - (first - u)) * channels + c] : 0.f;
       acc = fmaf(weight[(long long)c * taps + j], v, acc);
     }
-    out[(long long)t * channels + c] = from_float<T>(silu_f(acc));
+    out[(long long)t * channels + c] = from_float<T>(act ? silu_f(acc) : acc);
   }
 }
 
@@ -70,7 +73,8 @@ constexpr int kMaxTaps = 16;
 template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ in, long long in_stride, float* __restrict__ conv_state,
                                          long long state_stride, const int* __restrict__ q_start,
-                                         const int* __restrict__ state_slots, int num_slots, int channels, int taps) {
+                                         const int* __restrict__ state_slots, int num_slots, int channels, int taps,
+                                         const float* __restrict__ input_bias) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.y;
@@ -85,7 +89,8 @@ __global__ void conv_state_update_kernel(const T* __restrict__ in, long long in_
   for (int u = 0; u < kMaxTaps; ++u) {
     if (u < keep) {
       const int rel = count - keep + u;      // index among the step's tokens of this request
-      fresh[u] = rel >= 0 ? to_float(in[(long long)(first + rel) * in_stride + c]) : state[(long long)(u + count) * channels + c];
+      fresh[u] = rel >= 0 ? to_float(in[(long long)(first + rel) * in_stride + c]) + (input_bias ? input_bias[c] : 0.f)
+                          : state[(long long)(u + count) * channels + c];
     }
   }
 #pragma unroll
@@ -519,6 +524,73 @@ __global__ void gated_norm_kernel(const float* __restrict__ y, const T* __restri
   }
 }
 
+// ---------------------------------------------------------------------------
+// A gated linear recurrence with one state value per channel (a real-gated linear recurrent
+// unit).  Per request and channel c of block b = c / part, token after token:
+//   r = sigmoid(gates[t, b, k] + gate_bias[b, k]),   i = sigmoid(gates[t, b, part + k] + gate_bias[b, part + k]),
+//   a = exp(rate[c] * r),   S <- a S + sqrt(1 - a^2) i u[t, c],   out[t, c] = out_scale * S * gelu(y[t, c] + y_bias[c])
+// with k = c % part, rate negative (so 0 < a <= 1) and the tanh form of GELU.  One thread per
+// (request, channel); everything that does not depend on S (gates, decay, input, the other
+// branch's activation) is computed for kScanBatch tokens at a time before their chain of
+// multiply-adds, so the loads and the transcendental functions of a batch overlap.  S comes from
+// and returns to state[slot * state_stride + c]; a request without a slot starts from zero and
+// stores nothing.  1 - a^2 is formed as -expm1(2 rate r), which keeps its digits where a is close to 1.
+// ---------------------------------------------------------------------------
+constexpr int kScanBatch = 8;
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+
+template <typename T>
+__global__ void gated_scan_kernel(const float* __restrict__ gates, const float* __restrict__ gate_bias,
+                                  const T* __restrict__ u, const T* __restrict__ y, long long y_stride,
+                                  const float* __restrict__ y_bias, const float* __restrict__ rate,
+                                  float* __restrict__ state, long long state_stride, int num_slots,
+                                  const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                                  T* __restrict__ out, float out_scale, int width, int part) {
+  pdl_launch_dependents();
+  const int r = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = c < width;
+  const int b = live ? c / part : 0, k = live ? c - b * part : 0;
+  const long long gate_row = 2ll * width;
+  const int ga = b * 2 * part + k, gi = ga + part;
+  const float bias_a = live ? gate_bias[ga] : 0.f, bias_i = live ? gate_bias[gi] : 0.f;
+  const float channel_rate = live ? rate[c] : 0.f, channel_bias = live ? y_bias[c] : 0.f;
+  pdl_wait();
+  if (!live) return;
+  const int first = q_start[r], last = q_start[r + 1];
+  if (last <= first) return;
+  const int slot = state_slots[r];
+  const bool kept = slot >= 0 && slot < num_slots;
+  float s = kept ? state[(long long)slot * state_stride + c] : 0.f;
+  for (int t0 = first; t0 < last; t0 += kScanBatch) {
+    float a[kScanBatch], in[kScanBatch], other[kScanBatch];
+#pragma unroll
+    for (int e = 0; e < kScanBatch; ++e) {
+      const int t = t0 + e;
+      if (t < last) {
+        const float gr = gates[t * gate_row + ga] + bias_a;
+        const float gin = gates[t * gate_row + gi] + bias_i;
+        const float log_a = channel_rate * sigmoid_f(gr);
+        a[e] = expf(log_a);
+        in[e] = sqrtf(-expm1f(2.f * log_a)) * sigmoid_f(gin) * to_float(u[(long long)t * width + c]);
+        other[e] = out_scale * gelu_tanh_f(to_float(y[(long long)t * y_stride + c]) + channel_bias);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < kScanBatch; ++e) {
+      const int t = t0 + e;
+      if (t < last) {
+        s = fmaf(a[e], s, in[e]);
+        out[(long long)t * width + c] = from_float<T>(s * other[e]);
+      }
+    }
+  }
+  if (kept) state[(long long)slot * state_stride + c] = s;
+}
+
 }  // namespace einf
 
 using namespace einf;
@@ -527,7 +599,8 @@ extern "C" int einf_conv_silu(const void* in, int dtype, long long in_stride, co
                               float* conv_state, long long state_stride, const int* seq_of_token, const int* q_start,
                               const int* state_slots, int num_slots, int num_requests, void* out, int channels,
                               int taps, int num_tokens, const void* dt_in, const float* dt_bias, const float* a_log,
-                              float* dt_out, float* decay_out, int heads, cudaStream_t stream) {
+                              float* dt_out, float* decay_out, int heads, int act, const float* input_bias,
+                              cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (taps < 1 || taps > kMaxTaps || channels <= 0 || num_requests > 65535) return (int)cudaErrorInvalidValue;
   const int threads = 256;
@@ -538,11 +611,11 @@ extern "C" int einf_conv_silu(const void* in, int dtype, long long in_stride, co
     cudaError_t e = launch_pdl(conv_silu_kernel<T>, (int)blocks, threads, 0, stream, (const T*)in, in_stride, weight,
                                bias, (const float*)conv_state, state_stride, seq_of_token, q_start, state_slots,
                                num_slots, (T*)out, channels, taps, num_tokens, (const T*)dt_in, dt_bias, a_log, dt_out,
-                               decay_out, heads);
+                               decay_out, heads, act, input_bias);
     if (e != cudaSuccess || taps == 1) return (int)e;
     const dim3 grid((channels + 127) / 128, num_requests);
     return (int)launch_pdl(conv_state_update_kernel<T>, grid, 128, 0, stream, (const T*)in, in_stride, conv_state,
-                           state_stride, q_start, state_slots, num_slots, channels, taps);
+                           state_stride, q_start, state_slots, num_slots, channels, taps, input_bias);
   })
 }
 
@@ -647,5 +720,21 @@ extern "C" int einf_gated_norm(const float* y, const void* gate, int dtype, long
   EINF_DISPATCH_2(dtype, T, {
     return (int)launch_pdl(gated_norm_kernel<T>, (int)blocks, threads, 0, stream, y, (const T*)gate, gate_stride, weight,
                            (T*)out, width, parts, eps, gate_first, gate_kind);
+  })
+}
+
+extern "C" int einf_gated_scan(const float* gates, const float* gate_bias, const void* u, const void* y, int dtype,
+                               long long y_stride, const float* y_bias, const float* rate, float* state,
+                               long long state_stride, int num_slots, const int* q_start, const int* state_slots,
+                               int num_requests, void* out, float out_scale, int width, int blocks,
+                               cudaStream_t stream) {
+  if (num_requests == 0 || width == 0) return 0;
+  if (blocks <= 0 || width % blocks || num_requests > 65535) return (int)cudaErrorInvalidValue;
+  const int threads = 128;
+  const dim3 grid((width + threads - 1) / threads, num_requests);
+  EINF_DISPATCH_2(dtype, T, {
+    return (int)launch_pdl(gated_scan_kernel<T>, grid, threads, 0, stream, gates, gate_bias, (const T*)u, (const T*)y,
+                           y_stride, y_bias, rate, state, state_stride, num_slots, q_start, state_slots, (T*)out,
+                           out_scale, width, width / blocks);
   })
 }

@@ -1,0 +1,325 @@
+// The residual stream between sublayers, for blocks that do more to it than add and normalise:
+//   - a residual multiplier on every sublayer's output,
+//   - a short causal convolution over time in front of a sublayer, in the launch of the norm,
+//   - a per-layer token input after the feed-forward,
+//   - a weighted sum over the results of all layers so far in place of the layer's own result.
+// The stream is 32-bit; pending sublayer outputs arrive as up to two terms, each a [T, H] matrix
+// (float or bfloat16) or the float partial sums [S, T, H] of a split-K product, and are added in
+// a fixed order: term a split by split, then term b, then scaled, then added to the row.  Every
+// row is computed by one CTA from the row's own request alone.
+#include "common.cuh"
+
+namespace einf {
+
+constexpr int kMaxTaps = 16;
+
+struct Pending {
+  const void* a;
+  int a_dtype, a_splits;
+  long long a_stride;
+  const void* b;
+  int b_dtype, b_splits;
+  long long b_stride;
+};
+
+__device__ __forceinline__ float pending_term(const void* p, int dtype, int splits, long long stride, size_t idx) {
+  if (dtype == kBFloat16) {
+    const __nv_bfloat16* q = (const __nv_bfloat16*)p + idx;
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) v += __bfloat162float(q[(size_t)s * stride]);
+    return v;
+  }
+  const float* q = (const float*)p + idx;
+  constexpr int kBatch = 8;             // the partial sums sit in L2: keep several loads in flight
+  float v = 0.f;
+  for (int s0 = 0; s0 < splits; s0 += kBatch) {
+    float part[kBatch];
+#pragma unroll
+    for (int e = 0; e < kBatch; ++e) part[e] = s0 + e < splits ? q[(size_t)(s0 + e) * stride] : 0.f;
+#pragma unroll
+    for (int e = 0; e < kBatch; ++e) v += part[e];
+  }
+  return v;
+}
+
+__device__ __forceinline__ float pending_sum(const Pending& p, size_t idx) {
+  float v = 0.f;
+  if (p.a) v = pending_term(p.a, p.a_dtype, p.a_splits, p.a_stride, idx);
+  if (p.b) v += pending_term(p.b, p.b_dtype, p.b_splits, p.b_stride, idx);
+  return v;
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// ---------------------------------------------------------------------------
+// residual[t] += scale * pending[t];  h = residual[t] * rsqrt(mean(residual[t]^2) + eps) * weight
+// and then one of
+//   mode 0  out[t] = h (no convolution), or h * (1 + w[:, 0]) (a convolution of one tap)
+//   mode 1  every request brings one token: out[t] = h + sum_j w[:, j] line[j] with line = the
+//           request's state rows followed by h; the state moves on by one row in the same launch
+//   mode 2  h goes to `scratch` (floats) for the two kernels below, which see a request's other
+//           tokens of the step
+// One CTA per token; the row lives in shared memory between the two passes.
+// ---------------------------------------------------------------------------
+template <typename TOut>
+__global__ void norm_row_kernel(const __grid_constant__ Pending pending, float scale, float* __restrict__ residual,
+                                const float* __restrict__ weight, float eps, const float* __restrict__ conv_weight,
+                                int taps, float* __restrict__ conv_state, long long state_stride, int num_slots,
+                                const int* __restrict__ seq_of_token, const int* __restrict__ state_slots,
+                                TOut* __restrict__ out, float* __restrict__ scratch, int hidden, int mode) {
+  extern __shared__ float smem[];
+  float* row = smem;
+  float* red = smem + hidden;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const size_t base = (size_t)t * hidden;
+  const bool adds = pending.a != nullptr || pending.b != nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = residual[base + c];
+    if (adds) {
+      v += scale * pending_sum(pending, base + c);
+      residual[base + c] = v;
+    }
+    row[c] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)hidden + eps);
+  if (mode == 2) {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) scratch[base + c] = row[c] * inv * weight[c];
+    return;
+  }
+  if (mode == 0) {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      float h = row[c] * inv * weight[c];
+      if (conv_weight) h = fmaf(conv_weight[c], h, h);
+      out[base + c] = from_float<TOut>(h);
+    }
+    return;
+  }
+  const int slot = state_slots[seq_of_token[t]];
+  float* state = (slot >= 0 && slot < num_slots) ? conv_state + (long long)slot * state_stride : nullptr;
+  const int keep = taps - 1;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float h = row[c] * inv * weight[c];
+    const float* w = conv_weight + (size_t)c * taps;
+    float acc = h;
+    float line[kMaxTaps];
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j)
+      if (j < keep) line[j] = state ? state[(size_t)j * hidden + c] : 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j)
+      if (j < keep) acc = fmaf(w[j], line[j], acc);
+    acc = fmaf(w[keep], h, acc);
+    out[base + c] = from_float<TOut>(acc);
+    if (state) {
+#pragma unroll
+      for (int j = 0; j < kMaxTaps; ++j)
+        if (j + 1 < keep) state[(size_t)j * hidden + c] = line[j + 1];
+      state[(size_t)(keep - 1) * hidden + c] = h;
+    }
+  }
+}
+
+// out[t, c] = h[t, c] + sum_j w[c, j] * h[t - (taps - 1) + j, c] over the tokens of t's request, with
+// the request's state rows (its last taps - 1 inputs, oldest first) in front of its first token.
+template <typename TOut>
+__global__ void conv_rows_kernel(const float* __restrict__ h, const float* __restrict__ conv_weight, int taps,
+                                 const float* __restrict__ conv_state, long long state_stride, int num_slots,
+                                 const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
+                                 const int* __restrict__ state_slots, TOut* __restrict__ out, int hidden,
+                                 int num_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long total = (long long)num_tokens * hidden;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / hidden);
+    const int c = (int)(idx - (long long)t * hidden);
+    const int r = seq_of_token[t];
+    const int first = q_start[r];
+    const int slot = state_slots[r];
+    const float* state = (slot >= 0 && slot < num_slots) ? conv_state + (long long)slot * state_stride : nullptr;
+    float acc = h[idx];
+    for (int j = 0; j < taps; ++j) {
+      const int src = t - (taps - 1) + j;
+      float v;
+      if (src >= first) v = h[(long long)src * hidden + c];
+      else v = state ? state[(long long)(taps - 1 - (first - src)) * hidden + c] : 0.f;
+      acc = fmaf(conv_weight[(long long)c * taps + j], v, acc);
+    }
+    out[idx] = from_float<TOut>(acc);
+  }
+}
+
+// Afterwards the request's last taps - 1 inputs become its state (a portion shorter than that keeps
+// the tail of the old state in front).  One thread per (request, channel).
+__global__ void conv_rows_state_kernel(const float* __restrict__ h, float* __restrict__ conv_state,
+                                       long long state_stride, int num_slots, const int* __restrict__ q_start,
+                                       const int* __restrict__ state_slots, int hidden, int taps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int slot = state_slots[r];
+  if (c >= hidden || slot < 0 || slot >= num_slots) return;
+  const int first = q_start[r], count = q_start[r + 1] - first;
+  if (count <= 0) return;
+  float* state = conv_state + (long long)slot * state_stride;
+  const int keep = taps - 1;
+  float fresh[kMaxTaps];
+#pragma unroll
+  for (int u = 0; u < kMaxTaps; ++u) {
+    if (u < keep) {
+      const int rel = count - keep + u;
+      fresh[u] = rel >= 0 ? h[(long long)(first + rel) * hidden + c] : state[(long long)(u + count) * hidden + c];
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kMaxTaps; ++u)
+    if (u < keep) state[(long long)u * hidden + c] = fresh[u];
+}
+
+// ---------------------------------------------------------------------------
+// The end of a layer.  One CTA per token, the row x in shared memory:
+//   x = residual[t] + scale * pending[t]
+//   token input (table != null):  s = gate x  [n];  g = gelu(s) * table[token]  [n];  y = proj_t^T g  [H];
+//                                 x += scale * y * rsqrt(mean(y^2) + eps) * norm
+//   depth average (history != null):  history[index + 1][t] = x;
+//                                 x = sum_(j <= index) w[j] history[j][t] + w[index + 1] x
+//   residual[t] = x
+// gate [n, H] and proj_t [n, H] are read along H, a warp per row of gate for s, a thread per
+// column for y; the arithmetic is 32-bit whatever the matrices' type.
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void stream_tail_kernel(float* __restrict__ residual, const __grid_constant__ Pending pending, float scale,
+                                   const int* __restrict__ token_ids, const TW* __restrict__ table,
+                                   const TW* __restrict__ gate, const TW* __restrict__ proj_t,
+                                   const float* __restrict__ norm, int side, int vocab, float eps,
+                                   float* __restrict__ history, int depth_index, const float* __restrict__ depth_weight,
+                                   long long history_stride, int hidden) {
+  extern __shared__ float smem[];
+  float* x = smem;                   // [hidden]
+  float* y = x + hidden;             // [hidden]
+  float* g = y + hidden;             // [side]
+  float* red = g + side;             // [33]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const size_t base = (size_t)t * hidden;
+  const bool adds = pending.a != nullptr || pending.b != nullptr;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = residual[base + c];
+    if (adds) v += scale * pending_sum(pending, base + c);
+    x[c] = v;
+  }
+  __syncthreads();
+  if (table) {
+    int token = token_ids[t];
+    token = token < 0 ? 0 : (token >= vocab ? vocab - 1 : token);     // a bad id was reported by the embedding
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int d = warp; d < side; d += warps) {
+      const TW* w = gate + (size_t)d * hidden;
+      float dot = 0.f;
+      for (int c = lane; c < hidden; c += 32) dot = fmaf(to_float(w[c]), x[c], dot);
+      dot = warp_sum(dot);
+      if (lane == 0) g[d] = gelu_tanh_f(dot) * to_float(table[(size_t)token * side + d]);
+    }
+    __syncthreads();
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      float acc = 0.f;
+      for (int d = 0; d < side; ++d) acc = fmaf(to_float(proj_t[(size_t)d * hidden + c]), g[d], acc);
+      y[c] = acc;
+      ss = fmaf(acc, acc, ss);
+    }
+    const float inv = rsqrtf(block_sum(ss, red) / (float)hidden + eps);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) x[c] = fmaf(scale * inv * norm[c], y[c], x[c]);
+    // every thread reads back the columns it wrote itself: no barrier is needed before the next loop
+  }
+  if (history) {
+    float* mine = history + (size_t)(depth_index + 1) * history_stride + base;
+    const float newest = depth_weight[depth_index + 1];
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = x[c];
+      mine[c] = v;
+      float acc = 0.f;
+      for (int j = 0; j <= depth_index; ++j) acc = fmaf(depth_weight[j], history[(size_t)j * history_stride + base + c], acc);
+      residual[base + c] = fmaf(newest, v, acc);
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) residual[base + c] = x[c];
+  }
+}
+
+static int row_threads(int hidden) {
+  int threads = 64;
+  while (threads < hidden / 4 && threads < 512) threads <<= 1;
+  return threads;
+}
+
+}  // namespace einf
+
+using namespace einf;
+
+extern "C" int einf_norm_conv(const void* pend_a, int a_dtype, int a_splits, long long a_stride, const void* pend_b,
+                              int b_dtype, int b_splits, long long b_stride, float scale, float* residual,
+                              const float* weight, float eps, const float* conv_weight, int taps, float* conv_state,
+                              long long state_stride, int num_slots, const int* seq_of_token, const int* q_start,
+                              const int* state_slots, int num_requests, void* out, int out_dtype, float* scratch,
+                              int num_tokens, int hidden, int single_tokens, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (taps > kMaxTaps || hidden <= 0 || num_requests > 65535) return (int)cudaErrorInvalidValue;
+  const Pending pending{pend_a, a_dtype, a_splits, a_stride, pend_b, b_dtype, b_splits, b_stride};
+  const bool conv = conv_weight != nullptr && taps > 1;
+  if (conv && (!conv_state || (!single_tokens && !scratch))) return (int)cudaErrorInvalidValue;
+  const int mode = !conv ? 0 : (single_tokens ? 1 : 2);
+  const int threads = row_threads(hidden);
+  const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+  EINF_DISPATCH_2(out_dtype, T, {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(norm_row_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    cudaError_t e = launch_pdl(norm_row_kernel<T>, num_tokens, threads, smem, stream, pending, scale, residual, weight,
+                               eps, conv_weight, taps, conv_state, state_stride, num_slots, seq_of_token, state_slots,
+                               (T*)out, scratch, hidden, mode);
+    if (e != cudaSuccess || mode != 2) return (int)e;
+    const long long total = (long long)num_tokens * hidden;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    e = launch_pdl(conv_rows_kernel<T>, (int)blocks, 256, 0, stream, (const float*)scratch, conv_weight, taps,
+                   (const float*)conv_state, state_stride, num_slots, seq_of_token, q_start, state_slots, (T*)out,
+                   hidden, num_tokens);
+    if (e != cudaSuccess) return (int)e;
+    const dim3 grid((hidden + 127) / 128, num_requests);
+    return (int)launch_pdl(conv_rows_state_kernel, grid, 128, 0, stream, (const float*)scratch, conv_state,
+                           state_stride, num_slots, q_start, state_slots, hidden, taps);
+  })
+}
+
+extern "C" int einf_stream_tail(float* residual, const void* pend_a, int a_dtype, int a_splits, long long a_stride,
+                                const void* pend_b, int b_dtype, int b_splits, long long b_stride, float scale,
+                                const int* token_ids, const void* table, const void* gate, const void* proj_t,
+                                int weight_dtype, const float* norm, int side, int vocab, float eps, float* history,
+                                int depth_index, const float* depth_weight, long long history_stride, int num_tokens,
+                                int hidden, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (hidden <= 0 || side < 0) return (int)cudaErrorInvalidValue;
+  const Pending pending{pend_a, a_dtype, a_splits, a_stride, pend_b, b_dtype, b_splits, b_stride};
+  const int threads = row_threads(hidden);
+  const size_t smem = (size_t)(2 * hidden + side + 33) * sizeof(float);
+  EINF_DISPATCH_2(weight_dtype, T, {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(stream_tail_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    return (int)launch_pdl(stream_tail_kernel<T>, num_tokens, threads, smem, stream, residual, pending, scale,
+                           token_ids, (const T*)table, (const T*)gate, (const T*)proj_t, norm, side, vocab, eps,
+                           history, depth_index, depth_weight, history_stride, hidden);
+  })
+}

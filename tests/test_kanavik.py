@@ -1,0 +1,441 @@
+"""The Kanavik decoder in the engine against the plain statement of ``kanavik_plain``.
+
+Small configurations of their own, random weights, every position of every
+request compared.  The scenarios run twice: on the CPU through the plain
+statements of the kernels (``kernel_references.emulate_kernels``: what is under
+test then is the configuration, the weights' names, the cache plan with pages and
+a state row per layer, batch packing, replay and scheduler), and, marked ``gpu``,
+on the kernels in float32 and bfloat16.
+"""
+from __future__ import annotations
+
+import json
+import math
+
+import numpy as np
+import pytest
+import torch
+from safetensors.torch import save_file
+
+import kanavik_plain
+import trace_tools
+from conftest import random_tokens
+from kernel_references import emulate_kernels
+
+
+def layer(heads, kv_heads, dim, vdim, size, rwidth, blocks, conv, ff, scale=0.4, left_scale=0.7, right_scale=1.3):
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if size is not None:
+        left["mask"] = {"size": size}
+    return {
+        "type": "parallel",
+        "mixer": {"left": left, "left_scale": left_scale, "right": {"width": rwidth, "blocks": blocks, "conv": conv},
+                  "right_scale": right_scale},
+        "mlp": None if ff is None else {"kind": "dense", "ff": ff},
+    }
+
+
+def model(width, vocab, layers, taps=3, side=6, mult=0.6, eps=1e-5, positions=512):
+    config = {"architecture": "Kanavik", "vocab": vocab, "width": width, "max_positions": positions,
+              "norm": {"eps": eps}, "residual_mult": mult, "layers": layers}
+    if taps is not None:
+        config["canon"] = {"taps": taps}
+    if side is not None:
+        config["token_side"] = {"dim": side}
+    return config
+
+
+CONFIGS = {
+    # layers that differ in every size, a layer without a feed-forward, windows that are no multiple of a page,
+    # a layer without a window
+    "mix": model(48, 97, [
+        layer(4, 2, 16, 24, 7, 40, 2, 3, 64),
+        layer(6, 3, 8, 8, 13, 24, 3, 2, None, scale=0.7, left_scale=1.1, right_scale=0.4),
+        layer(2, 1, 24, 16, None, 32, 4, 5, 40),
+        layer(4, 4, 8, 12, 21, 48, 1, 4, 56),
+    ], taps=3, side=6, mult=0.6),
+    # values the sizes above make unequal, here equal or 1: one head, one key/value head, one block, one tap,
+    # a window of one key, a token input of one value, multiplier and scales of one
+    "ones": model(40, 61, [
+        layer(1, 1, 24, 8, 1, 40, 1, 1, 48, left_scale=1.0, right_scale=1.0),
+        layer(3, 3, 8, 40, 64, 16, 16, 2, None),
+        layer(5, 1, 8, 8, 2, 8, 2, 3, 24),
+    ], taps=1, side=1, mult=1.0, eps=1e-6),
+    # no input convolution, no token input
+    "bare": model(32, 50, [layer(2, 1, 16, 16, 9, 32, 2, 4, 40), layer(2, 2, 16, 8, 5, 16, 1, 2, None)],
+                  taps=None, side=None, mult=0.5),
+    # head sizes of 64, windows longer than the tiles the attention kernel walks
+    "wide": model(64, 83, [
+        layer(4, 2, 64, 64, 150, 64, 2, 4, 96),
+        layer(2, 1, 64, 32, 33, 128, 4, 4, 96, scale=0.2),
+    ], taps=4, side=16, mult=0.5),
+}
+PAGE = {"mix": 4, "ones": 8, "bare": 16, "wide": 16}
+SINGLE = {
+    # one branch of the mixer at a time (the other's scale is zero), no feed-forward
+    "attention": model(32, 50, [layer(4, 2, 8, 16, 6, 16, 2, 2, None, left_scale=1.0, right_scale=0.0)], taps=None,
+                       side=None, mult=1.0),
+    "recurrence": model(32, 50, [layer(2, 1, 8, 8, 3, 32, 4, 4, None, left_scale=0.0, right_scale=1.0)], taps=None,
+                        side=None, mult=1.0),
+    "mlp": model(32, 50, [layer(1, 1, 8, 8, 2, 8, 1, 1, 80, left_scale=0.1, right_scale=0.1)], taps=None, side=None),
+    "input_conv": model(32, 50, [layer(1, 1, 8, 8, 4, 8, 1, 2, 24)], taps=4, side=None),
+    "token_input": model(32, 50, [layer(1, 1, 8, 8, 4, 8, 1, 2, 24), layer(1, 1, 8, 8, 4, 8, 1, 2, None)], taps=None,
+                         side=5),
+}
+
+
+def write_folder(folder, config, seed, weights=None):
+    folder.mkdir(parents=True, exist_ok=True)
+    weights = weights if weights is not None else kanavik_plain.random_model(config, seed)
+    (folder / "config.json").write_text(json.dumps(config))
+    save_file({k: v.contiguous() for k, v in weights.items()}, str(folder / "model.safetensors"))
+    return weights
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("kanavik")
+    made = {}
+    for index, (name, config) in enumerate({**CONFIGS, **SINGLE}.items()):
+        made[name] = (base / name, config, write_folder(base / name, config, 20 + index))
+    return made
+
+
+def expected_rows(config, weights, requests):
+    out = {}
+    for name, tokens in requests.items():
+        logits, _ = kanavik_plain.forward(config, weights, tokens)
+        for position in range(len(tokens)):
+            out[(name, position)] = logits[position].float().numpy()
+    return out
+
+
+def make_requests(config, lengths, seed=0):
+    return {f"r{i}": random_tokens(config["vocab"], n, seed * 100 + i) for i, n in enumerate(lengths)}
+
+
+def check(rows, expected, dtype):
+    assert set(rows) == set(expected)
+    size = math.sqrt(float(np.mean([np.var(v) for v in expected.values()])))
+    limit = 2e-4 if dtype == "float32" else 0.04
+    # the error of a row (mean taken off, root mean square) against the size of the logits
+    for key in sorted(expected):
+        difference = rows[key] - expected[key]
+        error = float(np.sqrt(np.mean((difference - difference.mean()) ** 2))) / size
+        assert np.isfinite(rows[key]).all() and error < limit, f"first wrong token: {key}, error {error:.2e}"
+
+
+def replay_modes(folder, config, weights, page, dtype, device, lengths=(1, 5, 9, 23, 37, 50)):
+    from einf_b200.engine.replay import TraceReplayer
+
+    requests = make_requests(config, lengths)
+    expected = expected_rows(config, weights, requests)
+    mixed_steps, most = trace_tools.mixed(requests, seed=3, page_round=page)
+    room = -(-max(lengths) // 64) * 64
+    traces = {
+        "whole": (trace_tools.whole(requests), room),
+        "tail": (trace_tools.last_one_by_one(requests, tail=12), room),
+        "portions": (trace_tools.in_portions(requests), room),
+        "mixed": (mixed_steps, most),
+    }
+    for mode, (steps, max_tokens) in traces.items():
+        replayer = TraceReplayer(folder, dtype, max_tokens, block_len=page, device=device, max_requests=4)
+        rows = trace_tools.run_steps(replayer, steps)
+        check(rows, expected, dtype)
+        for group in range(replayer.manager.num_groups):
+            assert replayer.manager.free_pages(group) == replayer.manager.group(group).num_pages, mode
+        replayer.manager.check_invariants()
+
+
+# ---------------------------------------------------------------------------
+# the configuration and the weights' names
+def test_configuration_names_every_tensor_of_the_design(folders):
+    from einf_b200.config import KanavikConfig, load_config
+    from einf_b200.parts.model import expected_tensors
+
+    for name, (folder, config, weights) in folders.items():
+        loaded = load_config(folder)
+        assert isinstance(loaded, KanavikConfig)
+        expected, optional = expected_tensors(loaded.model_spec())
+        assert set(expected) == set(weights) and not optional, name
+        for key, spec in expected.items():
+            assert tuple(spec.shape) == tuple(weights[key].shape), key
+    spec = load_config(folders["mix"][0]).model_spec()
+    assert [layer.block for layer in spec.layers] == ["prenorm_stream"] * 4
+    assert "feed_forward" not in spec.layers[1].parts and "feed_forward_conv" not in spec.layers[1].parts
+
+
+def test_a_layer_plans_pages_and_one_state_row(folders):
+    """The attention branch's pages (one group per window) and, in one row of floats per layer and
+    request, the convolutions' inputs, the recurrence's state and its convolution's inputs."""
+    from einf_b200.config import load_config
+    from einf_b200.parts.base import PagesAndState
+
+    with emulate_kernels():
+        from einf_b200.config.engine import EngineConfig
+        from einf_b200.engine.runner import ModelRunner
+
+        folder, config, _ = folders["mix"]
+        runner = ModelRunner.from_folder(folder, EngineConfig(dtype="float32", block_len=4, num_blocks=32, device="cpu",
+                                                              max_requests=3, use_cuda_graphs=False))
+    plan = runner.model.cache_plan
+    assert plan.group_windows == (7, 13, None, 21)
+    width, taps = config["width"], config["canon"]["taps"]
+    for entry, made in zip(plan.entries, config["layers"]):
+        assert isinstance(entry.need, PagesAndState)
+        right = made["mixer"]["right"]
+        convs = (2 if made["mlp"] is not None else 1) * (taps - 1) * width
+        assert entry.need.state.shape == (convs + right["width"] * right["conv"],)
+        assert entry.need.pages.value_size == made["mixer"]["left"]["vdim"]
+    assert runner.num_state_slots == 3 and len(runner.storage.state_tensors) == 4
+
+
+def test_configuration_refuses_what_the_design_does_not_have():
+    from einf_b200.config import ConfigError, config_from_dict
+
+    good = CONFIGS["mix"]
+    config_from_dict(good)
+
+    def broken(change):
+        data = json.loads(json.dumps(good))
+        change(data)
+        with pytest.raises(ConfigError):
+            config_from_dict(data)
+
+    broken(lambda d: d["layers"][0].update(type="attention"))
+    broken(lambda d: d["layers"][0]["mixer"].pop("right"))
+    broken(lambda d: d["layers"][0]["mixer"].pop("left_scale"))
+    broken(lambda d: d["layers"][1]["mixer"]["left"].update(kv_heads=4))      # heads not a multiple
+    broken(lambda d: d["layers"][2]["mixer"]["right"].update(blocks=5))       # width not a multiple
+    broken(lambda d: d["layers"][0]["mlp"].update(kind="moe"))
+    broken(lambda d: d["layers"][0]["mixer"]["left"].pop("scale"))
+    broken(lambda d: d.pop("max_positions"))
+    broken(lambda d: d["canon"].update(taps=0))
+    broken(lambda d: d["norm"].update(eps=0))
+
+
+def test_random_weights_mode_writes_a_folder_the_loader_takes(tmp_path):
+    from einf_b200.config import config_from_dict, load_config
+    from einf_b200.parts.model import expected_tensors
+    from einf_b200.weights import load_tensors, write_random_model
+
+    folder = write_random_model(tmp_path / "m", config_from_dict(CONFIGS["mix"]), seed=4)
+    config = load_config(folder)
+    expected, optional = expected_tensors(config.model_spec())
+    tensors = load_tensors(folder, expected, optional=optional)
+    assert set(tensors) == set(expected)
+    assert float(tensors["l2.dwa"].float()[-1]) > 0.7 and tensors["l2.dwa"].shape == (4,)
+    talk = tensors["l0.mix.left.talk"].float()
+    assert float(talk.diagonal().min()) > 0.3
+
+
+# ---------------------------------------------------------------------------
+# the engine on the plain statements of the kernels (CPU)
+@pytest.fixture()
+def emulated():
+    with emulate_kernels():
+        yield
+
+
+@pytest.mark.parametrize("name", sorted(SINGLE))
+def test_each_mechanism_alone_emulated(name, folders, emulated):
+    folder, config, weights = folders[name]
+    replay_modes(folder, config, weights, 4, "float32", "cpu", lengths=(1, 6, 19))
+
+
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_replay_modes_emulated(name, folders, emulated):
+    folder, config, weights = folders[name]
+    replay_modes(folder, config, weights, PAGE[name], "float32", "cpu", lengths=(1, 5, 9, 23, 37))
+
+
+def greedy_plain(config, weights, prompt, new):
+    tokens = list(prompt)
+    for _ in range(new):
+        logits, _ = kanavik_plain.forward(config, weights, tokens)
+        tokens.append(int(torch.argmax(logits[-1])))
+    return tokens[len(prompt):]
+
+
+def generation(folder, config, weights, dtype, device, lookahead=1, graphs=False):
+    from einf_b200.config.engine import EngineConfig
+    from einf_b200.engine import Engine
+
+    prompts = [random_tokens(config["vocab"], n, 50 + n) for n in (3, 11, 1, 17, 6, 9)]
+    engine = Engine.from_folder(folder, EngineConfig(
+        dtype=dtype, block_len=4, num_blocks=48, max_batch_len=16, max_prefill_chunk_len=5, max_requests=4,
+        device=device, use_cuda_graphs=graphs, decode_lookahead=lookahead))
+    got = engine.generate(prompts, 8)
+    assert engine.runner.num_state_slots == 4         # six requests through four slots: slots are used again
+    return prompts, got
+
+
+def test_greedy_generation_through_the_entry_point_emulated(folders, emulated):
+    folder, config, weights = folders["mix"]
+    prompts, got = generation(folder, config, weights, "float32", "cpu")
+    for prompt, tokens in zip(prompts, got):
+        assert tokens == greedy_plain(config, weights, prompt, 8)
+
+
+def test_command_line_runs_the_design(folders, emulated, capsys, tmp_path):
+    from einf_b200.cli.run_qwen import main
+
+    folder, config, weights = folders["mix"]
+    prompt = [5, 17, 3, 90, 4, 8, 2]
+    code = main(["--model-dir", str(folder), "--prompt-ids", ",".join(map(str, prompt)), "--dtype", "float32",
+                 "--max-new-len", "5", "--max-prefill-chunk-len", "3", "--block-len", "4", "--max-requests", "2",
+                 "--device", "cpu", "--compare-reference"], prog="run_model")
+    out = capsys.readouterr().out
+    assert code == 0, out
+    fields = dict(line.split(": ", 1) for line in out.splitlines() if ": " in line)
+    assert json.loads(fields["generated_ids"]) == greedy_plain(config, weights, prompt, 5)
+    assert fields["tokens_equal"] == "True" and fields["completion_reason"] == "length"
+    # random weights from a bare config.json of the design
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(CONFIGS["ones"]))
+    code = main(["--random-weights", "--config", str(path), "--seed", "3", "--prompt-ids", "7,8,9", "--dtype", "float32",
+                 "--max-new-len", "4", "--block-len", "8", "--device", "cpu"])
+    out = capsys.readouterr().out
+    assert code == 0 and "generated_ids: [" in out, out
+
+
+# ---------------------------------------------------------------------------
+# keys that decide a row.  The weights are made for it: no position vectors, no input convolution
+# and no token input, so a token's key depends on the token alone; queries are the negated keys,
+# which makes a token its own worst match, and token 1's embedding is the negative of token 0's,
+# which makes token 1 (the needle) the best match of token 0 (the asker) by far, while their values
+# differ.  An asker `size - 1` positions after a needle sees it, the asker one position later must
+# not.  Needles stand more than a window apart (no asker sees two) and so that the edges fall inside
+# pages and on their borders.
+def needle_model(size, heads=2, kv_heads=1, scale=1.5):
+    config = model(32, 40, [layer(heads, kv_heads, 16, 16, size, 16, 2, 2, None, scale=scale, left_scale=1.0,
+                                  right_scale=0.2)], taps=None, side=None, mult=1.0, positions=1024)
+    weights = kanavik_plain.random_model(config, 5)
+    weights["l0.mix.left.q"] = torch.cat([-weights["l0.mix.left.k"].view(kv_heads, 16, 32)[h // (heads // kv_heads)]
+                                          for h in range(heads)])
+    weights["pos"] = torch.zeros_like(weights["pos"])
+    weights["embed"][1] = -weights["embed"][0]
+    weights["l0.mix.left.talk"] = (torch.eye(heads) + 0.1).to(torch.bfloat16)
+    weights["l0.mix.left.sink"] = torch.zeros(heads, dtype=torch.bfloat16)
+    return config, weights
+
+
+def needle_tokens(size, needles, length):
+    tokens = [2 + (i * 7) % 37 for i in range(length)]
+    askers = []
+    for n in needles:
+        tokens[n] = 1
+        tokens[n + size - 1] = 0         # sees the needle at the window's far edge
+        tokens[n + size] = 0             # one position on: out of sight
+        askers.append((n + size - 1, n + size))
+    return tokens, askers
+
+
+def needle_check(tmp_path, dtype, device, size, page, needles, length):
+    from einf_b200.engine.replay import TraceReplayer
+
+    config, weights = needle_model(size)
+    folder = tmp_path / f"needle{size}"
+    write_folder(folder, config, 0, weights)
+    tokens, askers = needle_tokens(size, needles, length)
+    requests = {"n": tokens}
+    expected = expected_rows(config, weights, requests)
+    # the plain statement itself must feel the edge: one position on, the needle is out of sight
+    for inside, outside in askers:
+        assert np.abs(expected[("n", inside)] - expected[("n", outside)]).max() > 0.5
+    room = -(-length // 64) * 64
+    for steps in (trace_tools.whole(requests), trace_tools.last_one_by_one(requests, tail=length - needles[0] - 2),
+                  trace_tools.in_portions(requests, sizes=(size - 1, 2, size, 3, 2))):
+        replayer = TraceReplayer(folder, dtype, room, block_len=page, device=device)
+        check(trace_tools.run_steps(replayer, steps), expected, dtype)
+
+
+def test_a_key_at_the_windows_edge_decides_the_row_emulated(tmp_path, emulated):
+    # window 24, pages of 16: the second needle's edge is the page border at 48
+    needle_check(tmp_path, "float32", "cpu", 24, 16, needles=(0, 25, 60), length=90)
+
+
+def far_key_model():
+    """No window: a needle hundreds of positions back must still count, among fillers."""
+    config, weights = needle_model(None, heads=2, kv_heads=2, scale=3.0)
+    return config, weights
+
+
+def far_key_check(tmp_path, dtype, device):
+    from einf_b200.engine.replay import TraceReplayer
+
+    config, weights = far_key_model()
+    folder = tmp_path / "far"
+    write_folder(folder, config, 0, weights)
+    length = 330
+    tokens = [2 + (i * 7) % 37 for i in range(length)]
+    with_needle = list(tokens)
+    with_needle[4] = 1
+    with_needle[-1] = tokens[-1] = 0
+    with_needle[300] = tokens[300] = 0
+    requests = {"with": with_needle, "without": tokens}
+    expected = expected_rows(config, weights, requests)
+    assert np.abs(expected[("with", length - 1)] - expected[("without", length - 1)]).max() > 0.3
+    for steps in (trace_tools.whole(requests), trace_tools.last_one_by_one(requests, tail=40),
+                  trace_tools.in_portions(requests, sizes=(129, 2, 64, 3))):
+        replayer = TraceReplayer(folder, dtype, 704, block_len=16, device=device)
+        check(trace_tools.run_steps(replayer, steps), expected, dtype)
+
+
+def test_a_far_key_counts_emulated(tmp_path, emulated):
+    far_key_check(tmp_path, "float32", "cpu")
+
+
+# ---------------------------------------------------------------------------
+# the kernels (GPU)
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(SINGLE))
+def test_each_mechanism_alone(name, dtype, folders):
+    folder, config, weights = folders[name]
+    replay_modes(folder, config, weights, 4, dtype, "cuda:0", lengths=(1, 6, 19, 70))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_replay_modes(name, dtype, folders):
+    folder, config, weights = folders[name]
+    replay_modes(folder, config, weights, PAGE[name], dtype, "cuda:0", lengths=(1, 5, 9, 23, 37, 50, 131, 300))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("size,page,needles", [(24, 16, (0, 25, 60)), (136, 16, (1, 153, 300)), (16, 4, (0, 17, 35))])
+def test_a_key_at_the_windows_edge_decides_the_row(dtype, size, page, needles, tmp_path):
+    needle_check(tmp_path, dtype, "cuda:0", size, page, needles, needles[-1] + size + 5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_far_key_counts(dtype, tmp_path):
+    far_key_check(tmp_path, dtype, "cuda:0")
+
+
+@pytest.mark.gpu
+def test_long_decoding_keeps_the_state(folders):
+    """Three hundred tokens one by one after a short prompt: the recurrent state and the
+    convolutions' inputs are carried from step to step, the windows pass many times and their
+    pages come back to the pool."""
+    from einf_b200.engine.replay import TraceReplayer
+
+    folder, config, weights = folders["mix"]
+    requests = make_requests(config, [310], seed=7)
+    expected = expected_rows(config, weights, requests)
+    replayer = TraceReplayer(folder, "float32", 320, block_len=PAGE["mix"], device="cuda:0")
+    rows = trace_tools.run_steps(replayer, trace_tools.last_one_by_one(requests, tail=300))
+    check(rows, expected, "float32")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("lookahead,graphs", [(1, False), (1, True), (4, True)])
+def test_greedy_generation_through_the_entry_point(lookahead, graphs, folders):
+    folder, config, weights = folders["mix"]
+    prompts, got = generation(folder, config, weights, "float32", "cuda:0", lookahead, graphs)
+    for prompt, tokens in zip(prompts, got):
+        assert tokens == greedy_plain(config, weights, prompt, 8)
