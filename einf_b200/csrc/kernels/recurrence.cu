@@ -534,7 +534,9 @@ __global__ void gated_norm_kernel(const float* __restrict__ y, const T* __restri
 // branch's activation) is computed for kScanBatch tokens at a time before their chain of
 // multiply-adds, so the loads and the transcendental functions of a batch overlap.  S comes from
 // and returns to state[slot * state_stride + c]; a request without a slot starts from zero and
-// stores nothing.  1 - a^2 is formed as -expm1(2 rate r), which keeps its digits where a is close to 1.
+// stores nothing.  A channel that remembers for long has a within 1e-5 of 1, where a float keeps two or
+// three digits of 1 - a; so the kernel carries d = 1 - a = -expm1(rate r) instead, steps S <- S - d S + input,
+// and forms 1 - a^2 as d (2 - d): the decay keeps its digits however close to 1 it is.
 // ---------------------------------------------------------------------------
 constexpr int kScanBatch = 8;
 __device__ __forceinline__ float gelu_tanh_f(float z) {
@@ -566,7 +568,7 @@ __global__ void gated_scan_kernel(const float* __restrict__ gates, const float* 
   const bool kept = slot >= 0 && slot < num_slots;
   float s = kept ? state[(long long)slot * state_stride + c] : 0.f;
   for (int t0 = first; t0 < last; t0 += kScanBatch) {
-    float a[kScanBatch], in[kScanBatch], other[kScanBatch];
+    float d[kScanBatch], in[kScanBatch], other[kScanBatch];
 #pragma unroll
     for (int e = 0; e < kScanBatch; ++e) {
       const int t = t0 + e;
@@ -574,8 +576,8 @@ __global__ void gated_scan_kernel(const float* __restrict__ gates, const float* 
         const float gr = gates[t * gate_row + ga] + bias_a;
         const float gin = gates[t * gate_row + gi] + bias_i;
         const float log_a = channel_rate * sigmoid_f(gr);
-        a[e] = expf(log_a);
-        in[e] = sqrtf(-expm1f(2.f * log_a)) * sigmoid_f(gin) * to_float(u[(long long)t * width + c]);
+        d[e] = -expm1f(log_a);
+        in[e] = sqrtf(d[e] * (2.f - d[e])) * sigmoid_f(gin) * to_float(u[(long long)t * width + c]);
         other[e] = out_scale * gelu_tanh_f(to_float(y[(long long)t * y_stride + c]) + channel_bias);
       }
     }
@@ -583,7 +585,7 @@ __global__ void gated_scan_kernel(const float* __restrict__ gates, const float* 
     for (int e = 0; e < kScanBatch; ++e) {
       const int t = t0 + e;
       if (t < last) {
-        s = fmaf(a[e], s, in[e]);
+        s = fmaf(-d[e], s, s) + in[e];
         out[(long long)t * width + c] = from_float<T>(s * other[e]);
       }
     }

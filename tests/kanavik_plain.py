@@ -45,8 +45,8 @@ def causal_conv(h, weight, bias=None):
     return out
 
 
-def distance_slopes(heads):
-    return torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], dtype=F64)
+def distance_slopes(heads, dtype=F64):
+    return torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], dtype=dtype)
 
 
 def talking_sink_attention(h, w, m):
@@ -58,12 +58,12 @@ def talking_sink_attention(h, w, m):
     k = (h @ w["k"].T).view(length, kv_heads, dim)
     v = (h @ w["v"].T).view(length, kv_heads, vdim)
     per = heads // kv_heads
-    slopes = distance_slopes(heads)
-    out = torch.zeros(length, heads, vdim, dtype=F64)
+    slopes = distance_slopes(heads, h.dtype)
+    out = torch.zeros(length, heads, vdim, dtype=h.dtype)
     group = torch.arange(heads) // per                              # key/value head of each query head
     for i in range(length):
         first = 0 if size is None else max(0, i - size + 1)
-        distance = (i - torch.arange(first, i + 1)).to(F64)         # i - j for every visible j
+        distance = (i - torch.arange(first, i + 1)).to(h.dtype)         # i - j for every visible j
         raw = torch.einsum("hd,jhd->hj", q[i], k[first:i + 1][:, group]) * m["scale"]
         raw = raw - slopes[:, None] * distance[None, :]
         mixed = w["talk"] @ raw                                     # [H, keys]: score_h <- sum_g T[h, g] score_g
@@ -82,11 +82,11 @@ def gated_linear_recurrence(h, w, m):
     u = causal_conv(h @ w["x"].T + w["x.b"], w["conv"], w["conv.b"])
     part = width // blocks
     softplus = torch.log1p(torch.exp(w["lam"]))
-    state = torch.zeros(width, dtype=F64)
-    out = torch.zeros(length, width, dtype=F64)
+    state = torch.zeros(width, dtype=h.dtype)
+    out = torch.zeros(length, width, dtype=h.dtype)
     for t in range(length):
-        r = torch.zeros(width, dtype=F64)
-        i = torch.zeros(width, dtype=F64)
+        r = torch.zeros(width, dtype=h.dtype)
+        i = torch.zeros(width, dtype=h.dtype)
         for b in range(blocks):
             ub = u[t, b * part:(b + 1) * part]
             r[b * part:(b + 1) * part] = torch.sigmoid(w["ra"][b] @ ub + w["ra.b"][b])
@@ -118,10 +118,11 @@ def _sub(weights, prefix):
     return {k[len(prefix):]: v for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(config, weights, tokens, after="average"):
+def forward(config, weights, tokens, after="average", dtype=F64):
     """Logits [T, vocab] and the residual stream after every layer [layers, T, width] (``after``:
-    ``average``: what goes on to the next layer; ``result``: before the weighted sum)."""
-    w = {k: v.to(F64) for k, v in weights.items()}
+    ``average``: what goes on to the next layer; ``result``: before the weighted sum).  ``dtype``: the
+    arithmetic; float32 shows how far plain rounding alone moves a row (how well it is conditioned)."""
+    w = {k: v.to(dtype) for k, v in weights.items()}
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     length = tokens.shape[0]
     eps = float(config["norm"]["eps"])

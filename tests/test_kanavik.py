@@ -114,15 +114,47 @@ def make_requests(config, lengths, seed=0):
     return {f"r{i}": random_tokens(config["vocab"], n, seed * 100 + i) for i, n in enumerate(lengths)}
 
 
-def check(rows, expected, dtype):
+def row_errors(rows, expected):
+    """The error of every row (mean taken off, root mean square) against the size of the logits."""
     assert set(rows) == set(expected)
     size = math.sqrt(float(np.mean([np.var(v) for v in expected.values()])))
-    limit = 2e-4 if dtype == "float32" else 0.04
-    # the error of a row (mean taken off, root mean square) against the size of the logits
+    errors = {}
     for key in sorted(expected):
+        assert np.isfinite(rows[key]).all(), f"first wrong token: {key}"
         difference = rows[key] - expected[key]
-        error = float(np.sqrt(np.mean((difference - difference.mean()) ** 2))) / size
-        assert np.isfinite(rows[key]).all() and error < limit, f"first wrong token: {key}, error {error:.2e}"
+        errors[key] = float(np.sqrt(np.mean((difference - difference.mean()) ** 2))) / size
+    return errors
+
+
+def conditioning(config, weights, requests, expected):
+    """How far rounding alone moves every row: the plain statement in float32 against itself in float64.
+    (A token input of one value, for instance, is a sign function of its gate: rows near a zero of the
+    gate move a hundred times more than the others.)"""
+    rows = {}
+    for name, tokens in requests.items():
+        logits, _ = kanavik_plain.forward(config, weights, tokens, dtype=torch.float32)
+        for position in range(len(tokens)):
+            rows[(name, position)] = logits[position].numpy()
+    return row_errors(rows, expected)
+
+
+def check(rows, expected, dtype, plain32=None, whole=None, what=""):
+    """float32: every row within 2e-5 plus three times what the plain statement in float32 loses there
+    (1e-4 where that is not given).  bfloat16 rounds 65,536 times coarser and single rows of a narrow
+    model with random weights move by tens of percent, so there the rows are held as a whole: half of
+    them within 0.02 and nine in ten within 0.06 of the plain statement, and the same against the rows
+    that the whole prompts gave (``whole``), from which a schedule differs only by the order of additions."""
+    errors = row_errors(rows, expected)
+    if dtype == "float32":
+        for key, error in errors.items():
+            limit = 1e-4 if plain32 is None else 2e-5 + 3.0 * plain32[key]
+            assert error < limit, f"{what}: first wrong token: {key}, error {error:.2e}, limit {limit:.2e}"
+        return
+    for against, values in (("plain", errors), ("whole", row_errors(rows, whole) if whole is not None else None)):
+        if values is not None:
+            values = np.array(list(values.values()))
+            assert float(np.median(values)) < 0.02 and float(np.quantile(values, 0.9)) < 0.06, \
+                f"{what} against {against}: median {np.median(values):.2e}, nine in ten {np.quantile(values, 0.9):.2e}"
 
 
 def replay_modes(folder, config, weights, page, dtype, device, lengths=(1, 5, 9, 23, 37, 50)):
@@ -130,6 +162,7 @@ def replay_modes(folder, config, weights, page, dtype, device, lengths=(1, 5, 9,
 
     requests = make_requests(config, lengths)
     expected = expected_rows(config, weights, requests)
+    plain32 = conditioning(config, weights, requests, expected) if dtype == "float32" else None
     mixed_steps, most = trace_tools.mixed(requests, seed=3, page_round=page)
     room = -(-max(lengths) // 64) * 64
     traces = {
@@ -138,10 +171,12 @@ def replay_modes(folder, config, weights, page, dtype, device, lengths=(1, 5, 9,
         "portions": (trace_tools.in_portions(requests), room),
         "mixed": (mixed_steps, most),
     }
+    whole = None
     for mode, (steps, max_tokens) in traces.items():
         replayer = TraceReplayer(folder, dtype, max_tokens, block_len=page, device=device, max_requests=4)
         rows = trace_tools.run_steps(replayer, steps)
-        check(rows, expected, dtype)
+        check(rows, expected, dtype, plain32, whole, mode)
+        whole = rows if mode == "whole" else whole
         for group in range(replayer.manager.num_groups):
             assert replayer.manager.free_pages(group) == replayer.manager.group(group).num_pages, mode
         replayer.manager.check_invariants()
