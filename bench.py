@@ -670,6 +670,257 @@ def tepavik_kernels(peak: dict) -> dict:
     return out
 
 
+def kanavik_sizes(width: int, ff: int, heads: int, kv_heads: int, size: int, layers: int, vocab: int, window: int,
+                  positions: int) -> dict:
+    """A Kanavik configuration at the layer sizes of a Qwen2 model: every layer has windowed attention
+    with mixed scores and a gated linear recurrence as wide as the model side by side, a gated
+    feed-forward, input convolutions of four taps, a token input of 64 values and the depth average."""
+    blocks = heads if width % heads == 0 else 8
+    layer = {
+        "type": "parallel",
+        "mixer": {
+            "left": {"heads": heads, "kv_heads": kv_heads, "dim": size, "vdim": size, "scale": size ** -0.5,
+                     "mask": {"size": window}},
+            "left_scale": 1.0,
+            "right": {"width": width, "blocks": blocks, "conv": 4},
+            "right_scale": 1.0,
+        },
+        "mlp": {"kind": "dense", "ff": ff},
+    }
+    return {"architecture": "Kanavik", "vocab": vocab, "width": width, "max_positions": positions,
+            "norm": {"eps": 1e-6}, "residual_mult": 0.5, "canon": {"taps": 4}, "token_side": {"dim": 64},
+            "layers": [dict(layer) for _ in range(layers)]}
+
+
+def run_kanavik(args) -> dict:
+    """Prefill and decode throughput of the Kanavik design at the layer sizes of the 0.5B and 1.5B
+    models (random weights, eight layers unless --layers says otherwise, a window of 1,024 keys),
+    beside Qwen2 at the same width, heads, feed-forward width, layers and vocabulary; then the
+    design's own kernels alone, each beside the kernel of the Qwen2 or Tepavik path that does the
+    like job at the same sizes."""
+    import torch
+
+    from einf_b200.cache import CacheManager
+    from einf_b200.config import EngineConfig, config_from_dict
+    from einf_b200.engine import ModelRunner
+    from einf_b200.sampling import Sampler
+
+    peak = peaks()
+    layers = args.layers or 8
+    result = {"scenario": "kanavik", "layers": layers, "context": CONTEXT, "window": 1024}
+    shapes = {"0.5b": (896, 4864, 14, 2, 64), "1.5b": (1536, 8960, 12, 2, 128)}
+    if args.only == "decode":       # one small workload for a launch list
+        shapes = {"0.5b": shapes["0.5b"]}
+    for name, (width, ff, heads, kv_heads, size) in shapes.items():
+        qwen = dict(SIZES["1.5b"] if name == "1.5b" else QWEN25_05B, num_hidden_layers=layers, tie_word_embeddings=False)
+        vocab = qwen["vocab_size"]
+        ours = kanavik_sizes(width, ff, heads, kv_heads, size, layers, vocab, 1024, 16384)
+        for arch, cfg in (("kanavik", ours), ("qwen2", qwen)):
+            if arch == "qwen2" and args.only == "decode":
+                continue
+            pages = 64 * (CONTEXT // PAGE + 2) + 64
+            runner = ModelRunner.from_random(
+                config_from_dict(cfg), 0,
+                EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=pages, max_batch_len=8192,
+                             max_prefill_chunk_len=8192, max_requests=64))
+            manager = CacheManager(runner.group_specs(), runner.num_state_slots)
+            sampler = Sampler(runner.runtime.device, 64)
+            for tokens in (() if args.only == "decode" else (2048, 8192)):
+                timed = time_prefill(runner, sampler, manager, tokens, repeats=5)
+                result[f"{name}_{arch}_prefill{tokens}_ms"] = round(timed["ms"], 3)
+                result[f"{name}_{arch}_prefill{tokens}_tokens_per_s"] = round(tokens / (timed["ms"] * 1e-3))
+            for batch in ((args.batch,) if args.only == "decode" else (1, 8, 64)):
+                timed = time_decode(runner, sampler, manager, batch, CONTEXT, args.steps, args.warmup,
+                                    min_seconds=0.0 if args.only == "decode" else 0.2)
+                result[f"{name}_{arch}_decode_b{batch}_ms"] = round(timed["ms_per_step"], 3)
+                result[f"{name}_{arch}_decode_b{batch}_tokens_per_s"] = round(timed["tokens_per_s"], 1)
+                result[f"{name}_{arch}_decode_b{batch}_launches_per_step"] = timed["launches"] // max(1, args.steps)
+            del runner, manager, sampler
+            torch.cuda.empty_cache()
+    if args.only != "decode":
+        result["kernels"] = kanavik_kernels(peak)
+    return result
+
+
+def kanavik_kernels(peak: dict) -> dict:
+    """The design's kernels alone (microseconds per launch in a CUDA graph of launches on rotating
+    buffers larger than the L2) with the bytes or flops each must move, beside the like kernel of
+    the Qwen2 path (attention, norm, activation) or of the Tepavik path (convolution and scan)."""
+    import torch
+
+    from einf_b200 import ops
+
+    device = torch.device("cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    out: dict = {}
+    gbs, tflops = peak["hbm_gbs"], peak["bf16_tflops"]
+    turn = [0]
+
+    def rate(key, us, nbytes=0, flops=0):
+        out[key + "_us"] = round(us, 1)
+        if nbytes:
+            out[key + "_hbm_frac"] = round(nbytes / us / 1e3 / gbs, 3)
+        if flops:
+            out[key + "_flops_frac"] = round(flops / us / 1e6 / tflops, 4)
+
+    window = 1024
+    for width, ff, heads, kv_heads, size in ((896, 4864, 14, 2, 64), (1536, 8960, 12, 2, 128)):
+        ops.ensure_built(list(ops.attention_libraries(size, PAGE)) + ["recurrence", "pointwise", "stream", "attention_mixed"])
+        tag = f"w{width}"
+        slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], device=device)
+        talk = (torch.eye(heads, device=device) + 0.1 * torch.randn(heads, heads, device=device)).contiguous()
+        sink = torch.randn(heads, device=device)
+        # --- attention, prompt of 2,048 tokens, a window of 1,024 keys
+        tokens = 2048
+        pages = tokens // PAGE
+        launches = 8
+        k = torch.randn(pages * launches + 4, kv_heads, PAGE, size, device=device).bfloat16()
+        v = torch.randn_like(k)
+        q = torch.randn(tokens, heads, size, device=device).bfloat16()
+        o = torch.empty_like(q)
+        tables = [torch.arange(i * pages, (i + 1) * pages, dtype=torch.int32, device=device).view(1, -1) for i in range(launches)]
+        tiles = torch.tensor([[0, first, 128, first] for first in range(0, tokens, 128)], dtype=torch.int32, device=device)
+        seq0 = torch.zeros(tokens, dtype=torch.int32, device=device)
+        pos0 = torch.arange(tokens, dtype=torch.int32, device=device)
+        pairs = sum(min(i + 1, window) for i in range(tokens))
+        flops = 4 * heads * size * pairs
+
+        def mixed_prefill():
+            table = tables[turn[0] % launches]
+            turn[0] += 1
+            ops.paged_attention_mixed(q, k, v, table, seq0, pos0, o, size ** -0.5, window, slopes, talk, sink, 1.0, status)
+
+        def plain_prefill():
+            table = tables[turn[0] % launches]
+            turn[0] += 1
+            ops.paged_prefill_attention(q, k, v, table, tiles, o, size ** -0.5, window, status, cached_before=0)
+
+        rate(tag + "_prefill_attention_mixed", _graph_time_us(mixed_prefill, launches), flops=flops)
+        rate(tag + "_prefill_attention_qwen2_windowed", _graph_time_us(plain_prefill, launches), flops=flops)
+        del k, v
+        # --- attention, decode of 8 and 64 requests at 4,096 tokens: the window's keys and values are read
+        for batch in (8, 64):
+            context = CONTEXT
+            pages = context // PAGE
+            layer_bytes = 2 * batch * window * kv_heads * size * 2
+            launches = 8
+            k = torch.randn(pages * batch * launches + 2, kv_heads, PAGE, size, device=device).bfloat16()
+            v = torch.randn_like(k)
+            qd = torch.randn(batch, heads, size, device=device).bfloat16()
+            od = torch.empty_like(qd)
+            dtables = [torch.arange(i * pages * batch, (i + 1) * pages * batch, dtype=torch.int32, device=device).view(batch, pages)
+                       for i in range(launches)]
+            seq = torch.arange(batch, dtype=torch.int32, device=device)
+            positions = torch.full((batch,), context - 1, dtype=torch.int32, device=device)
+
+            def mixed_decode():
+                table = dtables[turn[0] % launches]
+                turn[0] += 1
+                ops.paged_attention_mixed(qd, k, v, table, seq, positions, od, size ** -0.5, window, slopes, talk, sink,
+                                          1.0, status)
+
+            def plain_decode():
+                table = dtables[turn[0] % launches]
+                turn[0] += 1
+                ops.paged_decode_attention_auto(qd, k, v, table, seq, positions, od, size ** -0.5, window, status,
+                                                max_context=context)
+
+            rate(f"{tag}_decode_attention_b{batch}_mixed", _graph_time_us(mixed_decode, launches), nbytes=layer_bytes)
+            rate(f"{tag}_decode_attention_b{batch}_qwen2_windowed", _graph_time_us(plain_decode, launches), nbytes=layer_bytes)
+            del k, v
+        # --- the recurrence, the norms and the activation: a prompt of 2,048 tokens, single tokens of 8 and 64 requests
+        blocks = heads if width % heads == 0 else 8
+        part = width // blocks
+        for what, lengths in (("prompt2048", [2048]), ("decode_b8", [1] * 8), ("decode_b64", [1] * 64)):
+            requests, tokens = len(lengths), sum(lengths)
+            copies = max(4, min(64, int(3e8 // max(1, tokens * width * 16))))
+            starts = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=device)
+            slots = torch.arange(requests, dtype=torch.int32, device=device)
+            seq = torch.repeat_interleave(torch.arange(requests, dtype=torch.int32, device=device),
+                                          torch.tensor(lengths, device=device)).to(torch.int32)
+            singles = tokens == requests
+            gates = [torch.randn(tokens, blocks, 2 * part, device=device) for _ in range(copies)]
+            u = [torch.randn(tokens, width, device=device).bfloat16() for _ in range(copies)]
+            yx = [torch.randn(tokens, 2 * width, device=device).bfloat16() for _ in range(copies)]
+            so = torch.empty(tokens, width, device=device, dtype=torch.bfloat16)
+            gate_bias = torch.randn(blocks, 2 * part, device=device)
+            y_bias, rate_v = torch.randn(width, device=device), -torch.rand(width, device=device)
+            state = torch.zeros(requests, width * 4, device=device)
+            conv_w, conv_b = torch.randn(width, 4, device=device) * 0.3, torch.randn(width, device=device)
+
+            def scan():
+                i = turn[0] % copies
+                turn[0] += 1
+                ops.gated_scan(gates[i], gate_bias, u[i], yx[i][:, :width], y_bias, rate_v, state[:, :width], starts, slots,
+                               so, 1.0, max_q_len=max(lengths))
+
+            moved = tokens * width * (8 + 2 + 2 + 2) + 2 * requests * width * 4
+            rate(f"{tag}_gated_scan_{what}", _graph_time_us(scan, copies), nbytes=moved)
+
+            def conv():
+                i = turn[0] % copies
+                turn[0] += 1
+                ops.conv_silu(yx[i][:, width:], conv_w, conv_b, state[:, width:].unflatten(1, (3, width)), seq, starts, slots,
+                              so, activation=False, input_bias=y_bias)
+
+            rate(f"{tag}_recurrence_conv_{what}", _graph_time_us(conv, copies), nbytes=tokens * width * 4 + 2 * requests * width * 12)
+            # the norm with the input convolution beside the plain add-and-norm
+            residual = [torch.randn(tokens, width, device=device) for _ in range(copies)]
+            pend = [torch.randn(tokens, width, device=device).bfloat16() for _ in range(copies)]
+            norm_w = torch.ones(width, device=device)
+            canon_w = torch.randn(width, 4, device=device) * 0.3
+            canon_state = torch.zeros(requests, 3, width, device=device)
+            h = torch.empty(tokens, width, device=device, dtype=torch.bfloat16)
+
+            def norm_conv():
+                i = turn[0] % copies
+                turn[0] += 1
+                ops.norm_conv([pend[i], pend[(i + 1) % copies]], 0.5, residual[i], norm_w, 1e-6, canon_w, canon_state, seq,
+                              starts, slots, h, single_tokens=singles)
+
+            def add_norm():
+                i = turn[0] % copies
+                turn[0] += 1
+                ops.add_rmsnorm(pend[i], residual[i], norm_w, 1e-6, h)
+
+            rate(f"{tag}_norm_conv_{what}", _graph_time_us(norm_conv, copies), nbytes=tokens * width * (8 + 4 + 2))
+            rate(f"{tag}_add_rmsnorm_qwen2_{what}", _graph_time_us(add_norm, copies), nbytes=tokens * width * (8 + 2 + 2))
+            # the end of a layer: pending output, token input and the average over eight layers' results
+            side = 64
+            table = torch.randn(4096, side, device=device).bfloat16()
+            gate_w, proj_t = torch.randn(side, width, device=device).bfloat16() * 0.03, torch.randn(side, width, device=device).bfloat16()
+            ids = torch.randint(0, 4096, (tokens,), device=device, dtype=torch.int32)
+            depth = 4
+            history = torch.randn(depth + 2, tokens, width, device=device)
+            dw = torch.randn(depth + 2, device=device)
+
+            def tail():
+                i = turn[0] % copies
+                turn[0] += 1
+                ops.stream_tail(residual[i], [pend[i]], 0.5, ids, (table, gate_w, proj_t, norm_w, 1e-6), (history, depth, dw))
+
+            rate(f"{tag}_stream_tail_{what}", _graph_time_us(tail, copies), nbytes=tokens * width * (8 + 2 + 4 * (depth + 2)))
+            # the gate's activation
+            gu = [torch.randn(tokens, 2 * ff, device=device).bfloat16() for _ in range(min(copies, 8))]
+            act = torch.empty(tokens, ff, device=device, dtype=torch.bfloat16)
+
+            def gelu_mul():
+                i = turn[0] % len(gu)
+                turn[0] += 1
+                ops.act_mul(gu[i], act, "gelu_tanh")
+
+            def silu_mul():
+                i = turn[0] % len(gu)
+                turn[0] += 1
+                ops.silu_mul(gu[i], act)
+
+            rate(f"{tag}_gelu_mul_{what}", _graph_time_us(gelu_mul, len(gu)), nbytes=tokens * ff * 6)
+            rate(f"{tag}_silu_mul_qwen2_{what}", _graph_time_us(silu_mul, len(gu)), nbytes=tokens * ff * 6)
+            del gates, u, yx, residual, pend, gu
+    out["status"] = int(status)
+    return out
+
+
 def bomipel_sizes(width: int, heads: int, kv_heads: int, size: int, ff: int, experts: int, top: int, kv_rank: int,
                   rot_dim: int, q_rank: int, layers: int, vocab: int, window: int, keep_first: int) -> dict:
     """A Bomipel configuration at the layer sizes of a Qwen2 model: latent attention and windowed
@@ -1254,7 +1505,7 @@ def main() -> int:
                         help="leave the 1.5B and 7B workloads out of `points` (they take about a minute)")
     parser.add_argument("--lookahead", type=int, default=8,
                         help="EngineConfig.decode_lookahead of the end-to-end run: decode steps per report to the host")
-    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention", "prefill-sizes", "tepavik", "bomipel", "bomipel-kernels"), default="default",
+    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention", "prefill-sizes", "tepavik", "bomipel", "bomipel-kernels", "kanavik", "kanavik-kernels"), default="default",
                         help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
                              "cache pressure at 7B sizes, decode rooflines at 1.5B and 7B sizes; each prints "
                              "its own JSON line")
@@ -1290,7 +1541,8 @@ def main() -> int:
             line["config"]["sizes_7b"] = "L28 H3584 Hq28 Hkv4 D128 I18944 V152064 untied"
         print(json.dumps(line))
         return 0
-    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes, "decode-contexts": run_decode_contexts, "decode-attention": run_decode_attention, "prefill-sizes": run_prefill_sizes, "tepavik": run_tepavik, "bomipel": run_bomipel,
+    scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes, "decode-contexts": run_decode_contexts, "decode-attention": run_decode_attention, "prefill-sizes": run_prefill_sizes, "tepavik": run_tepavik, "bomipel": run_bomipel, "kanavik": run_kanavik,
+                 "kanavik-kernels": lambda args: {"scenario": "kanavik-kernels", "kernels": kanavik_kernels(peaks())},
                  "bomipel-kernels": lambda args: {"scenario": "bomipel-kernels", "kernels": bomipel_kernels(peaks())},
                  "sampling": run_sampling, "prefill-attention": run_prefill_attention}
     if args.scenario in scenarios:
