@@ -1,0 +1,420 @@
+// Score-mixing attention over the paged cache (the statement is at the top of attention_mixed.cu), tiled:
+// a CTA takes `rows` consecutive queries of one request with all their heads and walks the keys that
+// any of them sees in tiles of 64, so a key or value row is read once for all of them.  Per tile and
+// key/value head the keys go to shared memory as floats and every warp computes raw scores for a
+// (head, four queries) task, a lane per pair of keys (lane and lane + 32: rows 4 floats apart in the
+// padded tile, so a quarter warp's 16-byte reads fall into different banks).  Then a thread per
+// (query, key pair) takes the distance off, mixes the heads' scores from registers (the mixing matrix
+// is padded to HEADS_PAD columns, the unroll) and masks; then a warp per (head, query) row updates the
+// running maximum and sum and leaves the weights; then, per key/value head again, the values go to
+// shared memory and every warp adds its tasks' weighted values into registers, a lane per value column.
+// Scores, weights, sums and the output are 32-bit.  With several splits (grid.y) each CTA takes a share
+// of the key tiles and leaves (maximum, sum, unnormalised output); a second kernel joins them and the
+// sink.  Queries that come alone (decoding) use the same kernel with one query a task.
+// Compiled per HEADS_PAD (4, 8, 16 or 32 >= heads).
+#include "common.cuh"
+
+#ifndef HEADS_PAD
+#error "compile with -DHEADS_PAD=<4|8|16|32>"
+#endif
+
+namespace einf {
+
+constexpr int kTiledThreads = 256;
+constexpr int kTiledWarps = kTiledThreads / 32;
+constexpr int kKeyTile = 64;
+constexpr int kHP = HEADS_PAD;
+
+struct MixedTiledArgs {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  const int* block_table;
+  int table_width;
+  const int* seq_of_token;
+  const int* positions;
+  const int* q_tiles;        // [tiles, 4]: request, first token, rows, first position (tasks of four queries)
+  const int* single_tokens;  // token indices (tasks of one query); null: token = block
+  void* out;
+  int heads, kv_heads, dim, vdim, page_size, num_pages;
+  float scale;
+  int window;
+  const float* slopes;
+  const float* talk;
+  const float* sink;
+  float out_scale;
+  int rows, blocks_per_tile, splits;
+  float* part_acc;           // [splits, tokens, heads * vdim]
+  float* part_ml;            // [splits, tokens, heads, 2]
+  int num_tokens;
+  int* status;
+};
+
+struct BlockPlace {
+  int request, first_token, rows, first_position;
+};
+
+template <int QI>
+__device__ __forceinline__ BlockPlace block_place(const MixedTiledArgs& a) {
+  BlockPlace b;
+  if (QI == 1) {
+    const int t = a.single_tokens ? a.single_tokens[blockIdx.x] : (int)blockIdx.x;
+    b.request = a.seq_of_token[t];
+    b.first_token = t;
+    b.rows = 1;
+    b.first_position = a.positions[t];
+  } else {
+    const int tile = blockIdx.x / a.blocks_per_tile, sub = blockIdx.x - tile * a.blocks_per_tile;
+    const int* item = a.q_tiles + 4 * tile;
+    b.request = item[0];
+    b.first_token = item[1] + sub * a.rows;
+    b.rows = min(a.rows, item[2] - sub * a.rows);
+    b.first_position = item[3] + sub * a.rows;
+  }
+  return b;
+}
+
+template <typename T, int QI, int VD>
+__global__ void __launch_bounds__(kTiledThreads) paged_attention_mixed_tiled_kernel(const __grid_constant__ MixedTiledArgs a) {
+  constexpr int NT = QI == 1 ? 4 : 16 / VD;           // (head, query group) tasks a warp may hold
+  extern __shared__ float4 smem4[];
+  float* smem = (float*)smem4;
+  const int heads = a.heads, dim = a.dim, vdim = a.vdim, QB = a.rows;
+  const int per = heads / a.kv_heads;
+  const int nq = QB / QI;                             // query groups
+  const int ldk = dim + 4;
+  float* qs = smem;                                   // [heads * QB, dim], scaled
+  float* kv = qs + heads * QB * dim;                  // [64, ldk] keys, then [64, vdim] values
+  float* sc = kv + kKeyTile * max(ldk, vdim);         // [heads * QB, 64]
+  float* talk_s = sc + heads * QB * kKeyTile;         // [heads, kHP]
+  float* slope_s = talk_s + heads * kHP;              // [kHP]
+  float* top = slope_s + kHP;                         // [heads * QB]
+  float* total = top + heads * QB;
+  float* factor = total + heads * QB;
+
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const T* q = (const T*)a.q;
+  const T* k_cache = (const T*)a.k_cache;
+  const T* v_cache = (const T*)a.v_cache;
+  const bool joins = a.splits > 1;
+  for (int i = tid; i < heads * kHP; i += kTiledThreads) {
+    const int h = i / kHP, g = i - h * kHP;
+    talk_s[i] = g < heads ? (a.talk ? a.talk[h * heads + g] : (h == g ? 1.f : 0.f)) : 0.f;
+  }
+  for (int g = tid; g < kHP; g += kTiledThreads) slope_s[g] = (a.slopes && g < heads) ? a.slopes[g] : 0.f;
+  for (int r = tid; r < heads * QB; r += kTiledThreads) {
+    const bool with_sink = a.sink && !joins;
+    top[r] = with_sink ? a.sink[r / QB] : -INFINITY;
+    total[r] = with_sink ? 1.f : 0.f;
+  }
+  pdl_wait();
+  const BlockPlace place = block_place<QI>(a);
+  if (place.rows <= 0) return;
+  const int rows = place.rows, p0 = place.first_position;
+  for (int idx = tid; idx < heads * QB * dim; idx += kTiledThreads) {
+    const int r = idx / dim, d = idx - r * dim;
+    const int h = r / QB, i = r - h * QB;
+    qs[idx] = i < rows ? to_float(q[((size_t)(place.first_token + i) * heads + h) * dim + d]) * a.scale : 0.f;
+  }
+  const int hi = p0 + rows - 1;
+  const int lo = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
+  const int tiles_total = (hi - lo + kKeyTile) / kKeyTile;
+  const int tiles_each = (tiles_total + a.splits - 1) / a.splits;
+  const int tile_first = blockIdx.y * tiles_each, tile_last = min(tiles_total, tile_first + tiles_each);
+  const int* table = a.block_table + (size_t)place.request * a.table_width;
+
+  float acc[NT][QI][VD];
+#pragma unroll
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int qi = 0; qi < QI; ++qi)
+#pragma unroll
+      for (int dd = 0; dd < VD; ++dd) acc[n][qi][dd] = 0.f;
+
+  for (int tile = tile_first; tile < tile_last; ++tile) {
+    const int j0 = lo + tile * kKeyTile;
+    const int count = min(kKeyTile, hi - j0 + 1);
+    // ---- raw scores, one key/value head after the other
+    for (int g = 0; g < a.kv_heads; ++g) {
+      __syncthreads();                                // kv is free (and, the first time, qs is written)
+      for (int idx = tid; idx < kKeyTile * dim; idx += kTiledThreads) {
+        const int key = idx / dim, d = idx - key * dim;
+        float value = 0.f;
+        if (key < count) {
+          const int j = j0 + key;
+          const int page = table[j / a.page_size];
+          if (page >= 0 && page < a.num_pages)
+            value = to_float(k_cache[(((size_t)page * a.kv_heads + g) * a.page_size + j % a.page_size) * dim + d]);
+          else if (d == 0) atomicOr(a.status, kStatusBadPage);
+        }
+        kv[key * ldk + d] = value;
+      }
+      __syncthreads();
+      for (int task = warp; task < per * nq; task += kTiledWarps) {
+        const int h = g * per + task / nq, iq = task % nq;
+        float s[QI][2];
+#pragma unroll
+        for (int qi = 0; qi < QI; ++qi) s[qi][0] = s[qi][1] = 0.f;
+        const float* k0 = kv + lane * ldk;
+        const float* k1 = kv + (lane + 32) * ldk;
+        const float* qr = qs + (size_t)(h * QB + iq * QI) * dim;
+        for (int d = 0; d < dim; d += 4) {
+          const float4 x0 = *(const float4*)(k0 + d), x1 = *(const float4*)(k1 + d);
+#pragma unroll
+          for (int qi = 0; qi < QI; ++qi) {
+            const float4 y = *(const float4*)(qr + qi * dim + d);
+            s[qi][0] = fmaf(y.x, x0.x, s[qi][0]); s[qi][0] = fmaf(y.y, x0.y, s[qi][0]);
+            s[qi][0] = fmaf(y.z, x0.z, s[qi][0]); s[qi][0] = fmaf(y.w, x0.w, s[qi][0]);
+            s[qi][1] = fmaf(y.x, x1.x, s[qi][1]); s[qi][1] = fmaf(y.y, x1.y, s[qi][1]);
+            s[qi][1] = fmaf(y.z, x1.z, s[qi][1]); s[qi][1] = fmaf(y.w, x1.w, s[qi][1]);
+          }
+        }
+#pragma unroll
+        for (int qi = 0; qi < QI; ++qi) {
+          float* row = sc + (size_t)(h * QB + iq * QI + qi) * kKeyTile;
+          row[lane] = s[qi][0];
+          row[lane + 32] = s[qi][1];
+        }
+      }
+    }
+    __syncthreads();
+    // ---- distance, mixing and mask: a warp per query, a lane per pair of keys
+    for (int i = warp; i < QB; i += kTiledWarps) {
+      const int position = p0 + i;
+      float raw0[kHP], raw1[kHP];
+      const float away0 = (float)(position - (j0 + lane)), away1 = (float)(position - (j0 + lane + 32));
+#pragma unroll
+      for (int g = 0; g < kHP; ++g) {
+        if (g < heads) {
+          const float* row = sc + (size_t)(g * QB + i) * kKeyTile;
+          raw0[g] = row[lane] - slope_s[g] * away0;
+          raw1[g] = row[lane + 32] - slope_s[g] * away1;
+        } else {
+          raw0[g] = raw1[g] = 0.f;
+        }
+      }
+      const int reach = a.window > 0 ? position - a.window : -1;       // the last key out of sight
+      const bool see0 = i < rows && j0 + lane <= position && j0 + lane > reach;
+      const bool see1 = i < rows && j0 + lane + 32 <= position && j0 + lane + 32 > reach;
+      for (int h = 0; h < heads; ++h) {
+        const float4* mix = (const float4*)(talk_s + h * kHP);
+        float m0 = 0.f, m1 = 0.f;
+#pragma unroll
+        for (int g4 = 0; g4 < kHP / 4; ++g4) {
+          const float4 w = mix[g4];
+          m0 = fmaf(w.x, raw0[4 * g4], m0); m0 = fmaf(w.y, raw0[4 * g4 + 1], m0);
+          m0 = fmaf(w.z, raw0[4 * g4 + 2], m0); m0 = fmaf(w.w, raw0[4 * g4 + 3], m0);
+          m1 = fmaf(w.x, raw1[4 * g4], m1); m1 = fmaf(w.y, raw1[4 * g4 + 1], m1);
+          m1 = fmaf(w.z, raw1[4 * g4 + 2], m1); m1 = fmaf(w.w, raw1[4 * g4 + 3], m1);
+        }
+        float* row = sc + (size_t)(h * QB + i) * kKeyTile;
+        row[lane] = see0 ? m0 : -INFINITY;
+        row[lane + 32] = see1 ? m1 : -INFINITY;
+      }
+    }
+    __syncthreads();
+    // ---- running maximum and sum, a warp per (head, query) row; the weights stay in place
+    for (int r = warp; r < heads * QB; r += kTiledWarps) {
+      float* row = sc + (size_t)r * kKeyTile;
+      const float s0 = row[lane], s1 = row[lane + 32];
+      const float best = warp_max(fmaxf(s0, s1));
+      const float before = top[r];
+      const float now = fmaxf(before, best);
+      const float w0 = s0 == -INFINITY ? 0.f : expf(s0 - now);
+      const float w1 = s1 == -INFINITY ? 0.f : expf(s1 - now);
+      row[lane] = w0;
+      row[lane + 32] = w1;
+      const float sum = warp_sum(w0 + w1);
+      if (lane == 0) {
+        const float f = before == -INFINITY ? 0.f : expf(before - now);
+        factor[r] = f;
+        total[r] = fmaf(total[r], f, sum);
+        top[r] = now;
+      }
+    }
+    // ---- values, one key/value head after the other
+    for (int g = 0; g < a.kv_heads; ++g) {
+      __syncthreads();                                // weights and factors are written; kv is free
+      for (int idx = tid; idx < kKeyTile * vdim; idx += kTiledThreads) {
+        const int key = idx / vdim, d = idx - key * vdim;
+        float value = 0.f;
+        if (key < count) {
+          const int j = j0 + key;
+          const int page = table[j / a.page_size];
+          if (page >= 0 && page < a.num_pages)
+            value = to_float(v_cache[(((size_t)page * a.kv_heads + g) * a.page_size + j % a.page_size) * vdim + d]);
+        }
+        kv[idx] = value;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int task = n * kTiledWarps + warp;
+        if (task >= heads * nq) continue;
+        const int h = task / nq, iq = task - h * nq;
+        if (h / per != g) continue;
+        const int r0 = h * QB + iq * QI;
+#pragma unroll
+        for (int qi = 0; qi < QI; ++qi) {
+          const float f = factor[r0 + qi];
+#pragma unroll
+          for (int dd = 0; dd < VD; ++dd) acc[n][qi][dd] *= f;
+        }
+        for (int key = 0; key < kKeyTile; key += 4) {
+          float v[4][VD];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int dd = 0; dd < VD; ++dd) {
+              const int d = lane + 32 * dd;
+              v[e][dd] = d < vdim ? kv[(key + e) * vdim + d] : 0.f;
+            }
+#pragma unroll
+          for (int qi = 0; qi < QI; ++qi) {
+            const float4 w = *(const float4*)(sc + (size_t)(r0 + qi) * kKeyTile + key);
+#pragma unroll
+            for (int dd = 0; dd < VD; ++dd) {
+              float o = acc[n][qi][dd];
+              o = fmaf(w.x, v[0][dd], o); o = fmaf(w.y, v[1][dd], o);
+              o = fmaf(w.z, v[2][dd], o); o = fmaf(w.w, v[3][dd], o);
+              acc[n][qi][dd] = o;
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();                                    // the statistics, also when there was no tile
+  const int outs = heads * vdim;
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    const int task = n * kTiledWarps + warp;
+    if (task >= heads * nq) continue;
+    const int h = task / nq, iq = task - h * nq;
+#pragma unroll
+    for (int qi = 0; qi < QI; ++qi) {
+      const int i = iq * QI + qi;
+      if (i >= rows) continue;
+      const int r = h * QB + i;
+      const size_t t = (size_t)place.first_token + i;
+#pragma unroll
+      for (int dd = 0; dd < VD; ++dd) {
+        const int d = lane + 32 * dd;
+        if (d >= vdim) continue;
+        if (joins) a.part_acc[((size_t)blockIdx.y * a.num_tokens + t) * outs + h * vdim + d] = acc[n][qi][dd];
+        else ((T*)a.out)[t * outs + h * vdim + d] = from_float<T>(acc[n][qi][dd] / total[r] * a.out_scale);
+      }
+      if (joins && lane == 0) {
+        float* ml = a.part_ml + (((size_t)blockIdx.y * a.num_tokens + t) * heads + h) * 2;
+        ml[0] = top[r];
+        ml[1] = total[r];
+      }
+    }
+  }
+}
+
+// out[t, h, :] = out_scale * sum_s acc_s exp(m_s - M) / (exp(sink_h - M) + sum_s l_s exp(m_s - M)) with M the
+// largest of the splits' maxima and the sink, splits in order.  The same blocks as the kernel above.
+template <typename T, int QI>
+__global__ void __launch_bounds__(kTiledThreads) mixed_join_kernel(const __grid_constant__ MixedTiledArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const BlockPlace place = block_place<QI>(a);
+  if (place.rows <= 0) return;
+  const int outs = a.heads * a.vdim;
+  for (int idx = threadIdx.x; idx < place.rows * outs; idx += kTiledThreads) {
+    const int i = idx / outs, o = idx - i * outs;
+    const int h = o / a.vdim;
+    const size_t t = (size_t)place.first_token + i;
+    float best = a.sink ? a.sink[h] : -INFINITY;
+    for (int s = 0; s < a.splits; ++s) best = fmaxf(best, a.part_ml[(((size_t)s * a.num_tokens + t) * a.heads + h) * 2]);
+    float sum = a.sink ? expf(a.sink[h] - best) : 0.f;
+    float value = 0.f;
+    for (int s = 0; s < a.splits; ++s) {
+      const float* ml = a.part_ml + (((size_t)s * a.num_tokens + t) * a.heads + h) * 2;
+      const float w = ml[0] == -INFINITY ? 0.f : expf(ml[0] - best);
+      sum = fmaf(ml[1], w, sum);
+      value = fmaf(a.part_acc[((size_t)s * a.num_tokens + t) * outs + o], w, value);
+    }
+    ((T*)a.out)[t * outs + o] = from_float<T>(value / sum * a.out_scale);
+  }
+}
+
+}  // namespace einf
+
+using namespace einf;
+
+static size_t tiled_bytes(int heads, int dim, int vdim, int rows) {
+  const size_t floats = (size_t)heads * rows * dim + (size_t)kKeyTile * (dim + 4 > vdim ? dim + 4 : vdim) +
+                        (size_t)heads * rows * kKeyTile + (size_t)heads * kHP + kHP + 3 * (size_t)heads * rows;
+  return floats * sizeof(float);
+}
+
+// Rows a CTA takes for tasks of four queries: the most of 16, 8, 4 whose tasks fit a warp's registers and
+// whose shared memory leaves room for two CTAs an SM, else the most that fits at all; 0: none does.
+static int tiled_rows(int heads, int dim, int vdim) {
+  const int value_lanes = (vdim + 31) / 32;
+  const int tasks = kTiledWarps * (16 / (value_lanes <= 1 ? 1 : value_lanes <= 2 ? 2 : 4));
+  for (size_t limit : {(size_t)100 * 1024, (size_t)220 * 1024})
+    for (int rows : {16, 8, 4})
+      if (heads * (rows / 4) <= tasks && tiled_bytes(heads, dim, vdim, rows) <= limit) return rows;
+  return 0;
+}
+
+template <typename T, int QI, int VD>
+static int launch_tiled(const MixedTiledArgs& a, int blocks, cudaStream_t stream) {
+  auto kernel = paged_attention_mixed_tiled_kernel<T, QI, VD>;
+  const size_t bytes = tiled_bytes(a.heads, a.dim, a.vdim, a.rows);
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return (int)e;
+  }
+  cudaError_t e = launch_pdl(kernel, dim3(blocks, a.splits), kTiledThreads, bytes, stream, a);
+  if (e != cudaSuccess || a.splits == 1) return (int)e;
+  return (int)launch_pdl(mixed_join_kernel<T, QI>, blocks, kTiledThreads, 0, stream, a);
+}
+
+// Rows per CTA for the given sizes (0: this kernel does not take them; 1 with `single`).
+extern "C" int einf_paged_attention_mixed_tiled_rows(int heads, int dim, int vdim, int single) {
+  if (heads <= 0 || heads > kHP || dim <= 0 || dim % 4 || vdim <= 0 || vdim > 128) return 0;
+  if (single) return tiled_bytes(heads, dim, vdim, 1) <= (size_t)220 * 1024 ? 1 : 0;
+  return tiled_rows(heads, dim, vdim);
+}
+
+// `items`: q_tiles [num_items, 4] with single == 0; token indices [num_items] (or null: tokens 0 .. num_items - 1)
+// with single != 0.  `splits` > 1 needs part_acc [splits, num_tokens, heads * vdim] and part_ml [splits, num_tokens, heads, 2].
+extern "C" int einf_paged_attention_mixed_tiled(const void* q, const void* k_cache, const void* v_cache, int dtype,
+                                                const int* block_table, int table_width, const int* seq_of_token,
+                                                const int* positions, const int* items, int num_items, int single,
+                                                void* out, int num_tokens, int heads, int kv_heads, int dim, int vdim,
+                                                int page_size, int num_pages, float scale, int window,
+                                                const float* slopes, const float* talk, const float* sink,
+                                                float out_scale, int splits, float* part_acc, float* part_ml,
+                                                int* status, cudaStream_t stream) {
+  if (num_items == 0) return 0;
+  const int rows = einf_paged_attention_mixed_tiled_rows(heads, dim, vdim, single);
+  if (rows == 0 || kv_heads <= 0 || heads % kv_heads || splits < 1 || splits > 65535 ||
+      (splits > 1 && (!part_acc || !part_ml)))
+    return (int)cudaErrorInvalidValue;
+  MixedTiledArgs a;
+  a.q = q; a.k_cache = k_cache; a.v_cache = v_cache; a.block_table = block_table; a.table_width = table_width;
+  a.seq_of_token = seq_of_token; a.positions = positions;
+  a.q_tiles = single ? nullptr : items; a.single_tokens = single ? items : nullptr;
+  a.out = out; a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.page_size = page_size;
+  a.num_pages = num_pages; a.scale = scale; a.window = window; a.slopes = slopes; a.talk = talk; a.sink = sink;
+  a.out_scale = out_scale; a.rows = rows; a.blocks_per_tile = single ? 1 : (128 + rows - 1) / rows; a.splits = splits;
+  a.part_acc = part_acc; a.part_ml = part_ml; a.num_tokens = num_tokens; a.status = status;
+  const int blocks = num_items * a.blocks_per_tile;
+  const int value_lanes = (vdim + 31) / 32;
+#define EINF_TILED(QI, VD) EINF_DISPATCH_2(dtype, T, { return launch_tiled<T, QI, VD>(a, blocks, stream); })
+  if (single) {
+    if (value_lanes <= 1) EINF_TILED(1, 1)
+    if (value_lanes <= 2) EINF_TILED(1, 2)
+    EINF_TILED(1, 4)
+  }
+  if (value_lanes <= 1) EINF_TILED(4, 1)
+  if (value_lanes <= 2) EINF_TILED(4, 2)
+  EINF_TILED(4, 4)
+#undef EINF_TILED
+}

@@ -530,7 +530,7 @@ __global__ void gated_norm_kernel(const float* __restrict__ y, const T* __restri
 //   r = sigmoid(gates[t, b, k] + gate_bias[b, k]),   i = sigmoid(gates[t, b, part + k] + gate_bias[b, part + k]),
 //   a = exp(rate[c] * r),   S <- a S + sqrt(1 - a^2) i u[t, c],   out[t, c] = out_scale * S * gelu(y[t, c] + y_bias[c])
 // with k = c % part, rate negative (so 0 < a <= 1) and the tanh form of GELU.  One thread per
-// (request, channel); everything that does not depend on S (gates, decay, input, the other
+// (request, segment, channel); everything that does not depend on S (gates, decay, input, the other
 // branch's activation) is computed for kScanBatch tokens at a time before their chain of
 // multiply-adds, so the loads and the transcendental functions of a batch overlap.  S comes from
 // and returns to state[slot * state_stride + c]; a request without a slot starts from zero and
@@ -544,41 +544,84 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 
-template <typename T>
-__global__ void gated_scan_kernel(const float* __restrict__ gates, const float* __restrict__ gate_bias,
-                                  const T* __restrict__ u, const T* __restrict__ y, long long y_stride,
-                                  const float* __restrict__ y_bias, const float* __restrict__ rate,
-                                  float* __restrict__ state, long long state_stride, int num_slots,
-                                  const int* __restrict__ q_start, const int* __restrict__ state_slots,
-                                  T* __restrict__ out, float out_scale, int width, int part) {
+// A long portion is cut into segments of `segment_len` tokens that run side by side, one thread per
+// (request, segment, channel).  The first pass runs every segment but a request's last from a zero
+// state and leaves the product P of its decays and its own contribution B; the emitting pass walks
+// the segments before its own (S <- P S + B, from the slot's state) and then runs its tokens.  A
+// request's last segment writes the state back.  With one segment the emitting pass is all there is.
+struct ScanArgs {
+  const float* gates;
+  const float* gate_bias;
+  const void* u;
+  const void* y;
+  long long y_stride;
+  const float* y_bias;
+  const float* rate;
+  float* state;
+  long long state_stride;
+  int num_slots;
+  const int* q_start;
+  const int* state_slots;
+  void* out;
+  float out_scale;
+  int width, part, segments, segment_len;
+  float* segment_keep;      // [requests * segments, width]: P
+  float* segment_add;       // [requests * segments, width]: B
+};
+
+template <typename T, bool kEmit>
+__global__ void __launch_bounds__(128) gated_scan_kernel(const __grid_constant__ ScanArgs a) {
   pdl_launch_dependents();
-  const int r = blockIdx.y;
+  const int r = blockIdx.z, seg = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int width = a.width, part = a.part;
   const bool live = c < width;
   const int b = live ? c / part : 0, k = live ? c - b * part : 0;
   const long long gate_row = 2ll * width;
   const int ga = b * 2 * part + k, gi = ga + part;
-  const float bias_a = live ? gate_bias[ga] : 0.f, bias_i = live ? gate_bias[gi] : 0.f;
-  const float channel_rate = live ? rate[c] : 0.f, channel_bias = live ? y_bias[c] : 0.f;
+  const float bias_a = live ? a.gate_bias[ga] : 0.f, bias_i = live ? a.gate_bias[gi] : 0.f;
+  const float channel_rate = live ? a.rate[c] : 0.f, channel_bias = (live && kEmit) ? a.y_bias[c] : 0.f;
+  const T* u = (const T*)a.u;
+  const T* y = (const T*)a.y;
+  T* out = (T*)a.out;
   pdl_wait();
   if (!live) return;
-  const int first = q_start[r], last = q_start[r + 1];
-  if (last <= first) return;
-  const int slot = state_slots[r];
-  const bool kept = slot >= 0 && slot < num_slots;
-  float s = kept ? state[(long long)slot * state_stride + c] : 0.f;
+  const int begin = a.q_start[r], end = a.q_start[r + 1];
+  const int first = begin + seg * a.segment_len;
+  if (first >= end) return;
+  const int last = min(end, first + a.segment_len);
+  const bool closes = last == end;                       // the request's last segment
+  if (!kEmit && closes) return;
+  const int slot = a.state_slots[r];
+  const bool kept = slot >= 0 && slot < a.num_slots;
+  float s = 0.f, keep = 1.f;
+  if (kEmit) {
+    s = kept ? a.state[(long long)slot * a.state_stride + c] : 0.f;
+    const size_t row0 = (size_t)r * a.segments;
+    for (int j0 = 0; j0 < seg; j0 += kScanBatch) {
+      float p[kScanBatch], q[kScanBatch];
+#pragma unroll
+      for (int e = 0; e < kScanBatch; ++e) {
+        const bool in = j0 + e < seg;
+        p[e] = in ? a.segment_keep[(row0 + j0 + e) * width + c] : 1.f;
+        q[e] = in ? a.segment_add[(row0 + j0 + e) * width + c] : 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < kScanBatch; ++e) s = fmaf(p[e], s, q[e]);
+    }
+  }
   for (int t0 = first; t0 < last; t0 += kScanBatch) {
     float d[kScanBatch], in[kScanBatch], other[kScanBatch];
 #pragma unroll
     for (int e = 0; e < kScanBatch; ++e) {
       const int t = t0 + e;
       if (t < last) {
-        const float gr = gates[t * gate_row + ga] + bias_a;
-        const float gin = gates[t * gate_row + gi] + bias_i;
+        const float gr = a.gates[t * gate_row + ga] + bias_a;
+        const float gin = a.gates[t * gate_row + gi] + bias_i;
         const float log_a = channel_rate * sigmoid_f(gr);
         d[e] = -expm1f(log_a);
         in[e] = sqrtf(d[e] * (2.f - d[e])) * sigmoid_f(gin) * to_float(u[(long long)t * width + c]);
-        other[e] = out_scale * gelu_tanh_f(to_float(y[(long long)t * y_stride + c]) + channel_bias);
+        if (kEmit) other[e] = a.out_scale * gelu_tanh_f(to_float(y[(long long)t * a.y_stride + c]) + channel_bias);
       }
     }
 #pragma unroll
@@ -586,11 +629,18 @@ __global__ void gated_scan_kernel(const float* __restrict__ gates, const float* 
       const int t = t0 + e;
       if (t < last) {
         s = fmaf(-d[e], s, s) + in[e];
-        out[(long long)t * width + c] = from_float<T>(s * other[e]);
+        if (kEmit) out[(long long)t * width + c] = from_float<T>(s * other[e]);
+        else keep = fmaf(-d[e], keep, keep);
       }
     }
   }
-  if (kept) state[(long long)slot * state_stride + c] = s;
+  if (kEmit) {
+    if (closes && kept) a.state[(long long)slot * a.state_stride + c] = s;
+  } else {
+    const size_t row = (size_t)r * a.segments + seg;
+    a.segment_keep[row * width + c] = keep;
+    a.segment_add[row * width + c] = s;
+  }
 }
 
 }  // namespace einf
@@ -728,15 +778,24 @@ extern "C" int einf_gated_norm(const float* y, const void* gate, int dtype, long
 extern "C" int einf_gated_scan(const float* gates, const float* gate_bias, const void* u, const void* y, int dtype,
                                long long y_stride, const float* y_bias, const float* rate, float* state,
                                long long state_stride, int num_slots, const int* q_start, const int* state_slots,
-                               int num_requests, void* out, float out_scale, int width, int blocks,
-                               cudaStream_t stream) {
+                               int num_requests, void* out, float out_scale, int width, int blocks, int segments,
+                               int segment_len, float* segment_keep, float* segment_add, cudaStream_t stream) {
   if (num_requests == 0 || width == 0) return 0;
-  if (blocks <= 0 || width % blocks || num_requests > 65535) return (int)cudaErrorInvalidValue;
+  if (blocks <= 0 || width % blocks || num_requests > 65535 || segments < 1 || segments > 65535 || segment_len < 1 ||
+      (segments > 1 && (!segment_keep || !segment_add)))
+    return (int)cudaErrorInvalidValue;
+  ScanArgs a;
+  a.gates = gates; a.gate_bias = gate_bias; a.u = u; a.y = y; a.y_stride = y_stride; a.y_bias = y_bias; a.rate = rate;
+  a.state = state; a.state_stride = state_stride; a.num_slots = num_slots; a.q_start = q_start;
+  a.state_slots = state_slots; a.out = out; a.out_scale = out_scale; a.width = width; a.part = width / blocks;
+  a.segments = segments; a.segment_len = segment_len; a.segment_keep = segment_keep; a.segment_add = segment_add;
   const int threads = 128;
-  const dim3 grid((width + threads - 1) / threads, num_requests);
+  const dim3 grid((width + threads - 1) / threads, segments, num_requests);
   EINF_DISPATCH_2(dtype, T, {
-    return (int)launch_pdl(gated_scan_kernel<T>, grid, threads, 0, stream, gates, gate_bias, (const T*)u, (const T*)y,
-                           y_stride, y_bias, rate, state, state_stride, num_slots, q_start, state_slots, (T*)out,
-                           out_scale, width, width / blocks);
+    if (segments > 1) {
+      cudaError_t e = launch_pdl(gated_scan_kernel<T, false>, grid, threads, 0, stream, a);
+      if (e != cudaSuccess) return (int)e;
+    }
+    return (int)launch_pdl(gated_scan_kernel<T, true>, grid, threads, 0, stream, a);
   })
 }

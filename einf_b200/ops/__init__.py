@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -1391,6 +1391,88 @@ def stream_tail(
 MIXED_MAX_HEADS = 32
 
 
+MIXED_TILED_TARGET_CTAS = 2 * 148     # the keys of a launch with fewer CTAs than this are split
+_mixed_join_scratch: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def mixed_tiled_variant(heads: int) -> str:
+    """The build of the tiled score-mixing kernel for ``heads`` query heads."""
+    return "HEADS_PAD=" + str(next(n for n in (4, 8, 16, 32) if n >= heads))
+
+
+def mixed_tiled_rows(heads: int, key_size: int, value_size: int, single: bool) -> int:
+    """Queries a CTA of the tiled score-mixing kernel takes for these sizes (0: it does not take them)."""
+    if heads > MIXED_MAX_HEADS:
+        return 0
+    fn = _fn("einf_paged_attention_mixed_tiled_rows", [c_int, c_int, c_int, c_int], mixed_tiled_variant(heads))
+    return int(fn(heads, key_size, value_size, int(single)))
+
+
+def mixed_tiled_splits(blocks: int, rows: int, window: Optional[int], max_context: int) -> int:
+    """CTAs that share the keys of one block of ``rows`` queries: enough to fill the device when the
+    launch has few blocks, and no more than the 64-key tiles a query can see."""
+    if not max_context and not window:
+        return 1
+    keys = max_context or (1 << 30)
+    if window:
+        keys = min(keys, int(window) + rows - 1)
+    return max(1, min(-(-keys // 64), -(-MIXED_TILED_TARGET_CTAS // max(1, blocks)), 64))
+
+
+def _mixed_tiled(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, slopes, talk, sink,
+                 out_scale, status, q_tiles, single_tokens, num_singles, max_context) -> bool:
+    tokens, heads, key_size = q.shape
+    num_pages, kv_heads, page_size, _ = k_cache.shape
+    value_size = v_cache.shape[3]
+    num_tiles = q_tiles.shape[0]
+    if q_tiles.dtype != torch.int32 or q_tiles.dim() != 2 or q_tiles.shape[1] != 4:
+        raise ValueError("q_tiles must be int32 [tiles, 4]")
+    launches = []
+    if num_singles:
+        launches.append((single_tokens, num_singles, 1, mixed_tiled_rows(heads, key_size, value_size, True)))
+    if num_tiles:
+        launches.append((q_tiles, num_tiles, 0, mixed_tiled_rows(heads, key_size, value_size, False)))
+    if not launches or any(rows == 0 for _, _, _, rows in launches):
+        return False
+    variant = mixed_tiled_variant(heads)
+    fn = _fn(
+        "einf_paged_attention_mixed_tiled",
+        [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
+         c_void_p, c_void_p, c_void_p, c_void_p],
+        variant,
+    )
+    global launch_count
+    for items, count, single, rows in launches:
+        splits = mixed_tiled_splits(count * (1 if single else -(-128 // rows)), rows, window, max_context)
+        part_acc = part_ml = None
+        if splits > 1:
+            key = (str(q.device), splits, tokens, heads, value_size)
+            scratch = _mixed_join_scratch.get(key)
+            if scratch is None:
+                scratch = (torch.empty((splits, tokens, heads * value_size), dtype=torch.float32, device=q.device),
+                           torch.empty((splits, tokens, heads, 2), dtype=torch.float32, device=q.device))
+                if len(_mixed_join_scratch) > 16:
+                    _mixed_join_scratch.clear()
+                _mixed_join_scratch[key] = scratch
+            part_acc, part_ml = scratch
+        _check(
+            fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), _code(q),
+               _opt(block_table, "block_table", torch.int32), block_table.shape[1],
+               _opt(seq_of_token, "seq_of_token", torch.int32), _opt(positions, "positions", torch.int32),
+               _opt(items, "items", torch.int32), count, single, _dev(out, "out"), tokens, heads, kv_heads, key_size,
+               value_size, page_size, num_pages, float(scale), int(window or 0),
+               _opt(slopes, "slopes", torch.float32), _opt(talk, "talk", torch.float32),
+               _opt(sink, "sink", torch.float32), float(out_scale), splits,
+               _opt(part_acc, "part_acc", torch.float32), _opt(part_ml, "part_ml", torch.float32),
+               _dev(status, "status"), _stream()),
+            "paged_attention_mixed_tiled",
+        )
+        if splits > 1:
+            launch_count += 1      # the kernel that joins the splits
+    return True
+
+
 def paged_attention_mixed(
     q: torch.Tensor,
     k_cache: torch.Tensor,
@@ -1406,13 +1488,24 @@ def paged_attention_mixed(
     sink: Optional[torch.Tensor],
     out_scale: float,
     status: torch.Tensor,
+    q_tiles: Optional[torch.Tensor] = None,
+    single_tokens: Optional[torch.Tensor] = None,
+    num_singles: int = 0,
+    max_context: int = 0,
 ) -> None:
     """Causal (optionally windowed) attention over the paged cache in which all heads of a query are
     computed together: ``s_h(i, j) = scale q_h(i).k_g(j) - slopes[h] (i - j)``, then ``s_h <- sum_g talk[h,
     g] s_g`` over all query heads, then a softmax over the visible keys whose denominator also holds
     ``exp(sink[h])``, then ``out_h = out_scale * sum_j p_h(j) v_g(j)``.  ``slopes``, ``talk`` and ``sink``
     (float32 ``[H]``, ``[H, H]``, ``[H]``) are each optional.  ``q [T, H, D]``, caches ``[pages, G, page,
-    D]`` and ``[pages, G, page, V]``, ``out [T, H, V]``; scores, weights and sums are 32-bit."""
+    D]`` and ``[pages, G, page, V]``, ``out [T, H, V]``; scores, weights and sums are 32-bit.
+
+    With the step's split into ``q_tiles`` (int32 ``[tiles, 4]``: request, first token, rows, first position
+    of up to 128 rows of a request that brings several tokens) and ``num_singles`` requests that bring one
+    token (``single_tokens``: their token indices, or None when every token is one), the tiled kernel runs:
+    consecutive queries of a request share the keys and values they read, and the keys of few queries are
+    split over several CTAs (``max_context`` bounds the keys a query sees).  Without the split, or for
+    sizes the tiled kernel does not take, one CTA per token walks its keys alone."""
     tokens, heads, key_size = q.shape
     num_pages, kv_heads, page_size, size = k_cache.shape
     value_size = v_cache.shape[3]
@@ -1427,6 +1520,10 @@ def paged_attention_mixed(
     for name, t, shape in (("slopes", slopes, (heads,)), ("talk", talk, (heads, heads)), ("sink", sink, (heads,))):
         if t is not None and (t.dtype != torch.float32 or t.shape != shape):
             raise ValueError(f"{name} must be float32 {shape}")
+    if q_tiles is not None and _mixed_tiled(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale,
+                                            window, slopes, talk, sink, out_scale, status, q_tiles, single_tokens,
+                                            num_singles, max_context):
+        return
     fn = _fn(
         "einf_paged_attention_mixed",
         [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -1441,6 +1538,15 @@ def paged_attention_mixed(
            _opt(sink, "sink", torch.float32), float(out_scale), _dev(status, "status"), _stream()),
         "paged_attention_mixed",
     )
+
+
+GATED_SCAN_SEGMENT = 16      # tokens a thread of the gated scan takes, while that makes no more than 128 segments
+
+
+def gated_scan_plan(longest: int) -> Tuple[int, int]:
+    """(segments, tokens per segment) of the gated scan for a step whose longest portion has ``longest`` tokens."""
+    segment_len = max(GATED_SCAN_SEGMENT, 8 * -(-longest // (8 * 128)))
+    return max(1, -(-longest // segment_len)), segment_len
 
 
 def gated_scan(
@@ -1476,18 +1582,31 @@ def gated_scan(
         raise ValueError("u, y_raw and out are [tokens, width] of one dtype")
     if state.dtype != torch.float32 or state.shape[1] != width or state.stride(1) != 1:
         raise ValueError(f"state must be float32 [slots, {width}]")
+    requests = state_slots.shape[0]
+    if tokens == 0 or requests == 0:
+        return
+    segments, segment_len = gated_scan_plan(max_q_len or tokens)
+    segment_keep = segment_add = None
+    if segments > 1:
+        segment_keep = torch.empty((requests * segments, width), dtype=torch.float32, device=out.device)
+        segment_add = torch.empty_like(segment_keep)
     fn = _fn(
         "einf_gated_scan",
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
-         c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_int, c_void_p],
+         c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     )
     _check(
         fn(_dev(gates, "gates"), _dev(gate_bias, "gate_bias"), _dev(u, "u"), y_raw.data_ptr(), _code(u),
            _rows_of(y_raw, "y_raw"), y_bias.data_ptr(), _dev(rate, "rate"), state.data_ptr(), state.stride(0),
            state.shape[0], _opt(q_start, "q_start", torch.int32), _opt(state_slots, "state_slots", torch.int32),
-           state_slots.shape[0], _dev(out, "out"), float(out_scale), width, blocks, _stream()),
+           requests, _dev(out, "out"), float(out_scale), width, blocks, segments, segment_len,
+           _opt(segment_keep, "segment_keep", torch.float32), _opt(segment_add, "segment_add", torch.float32),
+           _stream()),
         "gated_scan",
     )
+    if segments > 1:
+        global launch_count
+        launch_count += 1      # the first pass over the segments
 
 
 FAST_ATTENTION_MAX_HEAD_SIZE = 128

@@ -48,6 +48,8 @@ LAUNCHERS = {
     "einf_norm_conv": "stream",
     "einf_stream_tail": "stream",
     "einf_paged_attention_mixed": "attention_mixed",
+    "einf_paged_attention_mixed_tiled": "attention_mixed_tiled",
+    "einf_paged_attention_mixed_tiled_rows": "attention_mixed_tiled",
     "einf_gated_scan": "recurrence",
     "einf_argmax": "sampling",
     "einf_sample": "sampling",

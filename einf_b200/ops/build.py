@@ -154,7 +154,8 @@ def kernel_include_dirs() -> list[str]:
 
 
 #: sources that are compiled once per value of a macro, and the values build_all() compiles
-SPECIALISED = {"attention_bf16": ("HEAD_SIZE", (64, 128)), "attention_tcgen05": ("HEAD_SIZE", (64, 128))}
+SPECIALISED = {"attention_bf16": ("HEAD_SIZE", (64, 128)), "attention_tcgen05": ("HEAD_SIZE", (64, 128)),
+               "attention_mixed_tiled": ("HEADS_PAD", (4, 8, 16, 32))}
 
 
 def split_variant(name: str) -> tuple[str, dict[str, str]]:

@@ -88,7 +88,10 @@ class PagedAttention(Mixer):
     @classmethod
     def kernel_libraries(cls, spec, runtime):
         if cls._mixes_scores(spec):
-            return ("pointwise", "attention_mixed", "gemm_simt") + cls._product_libraries(runtime)
+            tiled = ()
+            if int(spec["num_heads"]) <= ops.MIXED_MAX_HEADS:
+                tiled = ("attention_mixed_tiled:" + ops.mixed_tiled_variant(int(spec["num_heads"])),)
+            return ("pointwise", "attention_mixed", "gemm_simt") + tiled + cls._product_libraries(runtime)
         if cls._is_general(spec):
             fast = (f"attention_tcgen05:HEAD_SIZE={int(spec['head_size'])}",) \
                 if cls._general_on_tensor_cores(spec, runtime.dtype) else ()
@@ -221,6 +224,9 @@ class PagedAttention(Mixer):
         """The decode attention cuts a token's keys by the number of single tokens and the bucket
         of the longest context: kernel, cluster size and clusters per token."""
         singles = int(ctx.single_tokens.shape[0])
+        if self.mixes_scores:
+            # the tiled kernel splits the keys of single tokens by their number and the longest context
+            return ("mixed", ops.mixed_tiled_splits(singles, 1, self.window, ctx.max_context_len)) if singles else ()
         if not (self.fast or (self.general_fast and ops.has_tcgen05_attention(self.head_size, page_size))) or not singles:
             return ()
         context = ctx.max_context_len
@@ -243,6 +249,8 @@ class PagedAttention(Mixer):
             ops.paged_attention_mixed(
                 q, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, out, self.scale, self.window,
                 self.slopes, self.talk, self.sink, self.output_scale, ctx.status,
+                q_tiles=ctx.q_tiles, single_tokens=None if ctx.decode_only else ctx.single_tokens,
+                num_singles=int(ctx.single_tokens.shape[0]), max_context=ctx.max_context_len,
             )
             return
         if self.fast or (self.general_fast and ops.has_tcgen05_attention(self.head_size, cache.k.shape[2])):

@@ -413,7 +413,7 @@ def stream_tail(residual, pending, pending_scale, token_ids, side, depth):
 
 
 def paged_attention_mixed(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, slopes, talk,
-                          sink, out_scale, status):
+                          sink, out_scale, status, q_tiles=None, single_tokens=None, num_singles=0, max_context=0):
     tokens, num_heads, _ = q.shape
     _, num_kv_heads, page_size, _ = k_cache.shape
     groups = num_heads // num_kv_heads
