@@ -709,14 +709,14 @@ def run_kanavik(args) -> dict:
     layers = args.layers or 8
     result = {"scenario": "kanavik", "layers": layers, "context": CONTEXT, "window": 1024}
     shapes = {"0.5b": (896, 4864, 14, 2, 64), "1.5b": (1536, 8960, 12, 2, 128)}
-    if args.only == "decode":       # one small workload for a launch list
+    if args.only != "all":          # one small workload for a launch list
         shapes = {"0.5b": shapes["0.5b"]}
     for name, (width, ff, heads, kv_heads, size) in shapes.items():
         qwen = dict(SIZES["1.5b"] if name == "1.5b" else QWEN25_05B, num_hidden_layers=layers, tie_word_embeddings=False)
         vocab = qwen["vocab_size"]
         ours = kanavik_sizes(width, ff, heads, kv_heads, size, layers, vocab, 1024, 16384)
         for arch, cfg in (("kanavik", ours), ("qwen2", qwen)):
-            if arch == "qwen2" and args.only == "decode":
+            if arch == "qwen2" and args.only != "all":
                 continue
             pages = 64 * (CONTEXT // PAGE + 2) + 64
             runner = ModelRunner.from_random(
@@ -725,11 +725,11 @@ def run_kanavik(args) -> dict:
                              max_prefill_chunk_len=8192, max_requests=64))
             manager = CacheManager(runner.group_specs(), runner.num_state_slots)
             sampler = Sampler(runner.runtime.device, 64)
-            for tokens in (() if args.only == "decode" else (2048, 8192)):
-                timed = time_prefill(runner, sampler, manager, tokens, repeats=5)
+            for tokens in {"decode": (), "prefill": (2048,)}.get(args.only, (2048, 8192)):
+                timed = time_prefill(runner, sampler, manager, tokens, repeats=2 if args.only == "prefill" else 5)
                 result[f"{name}_{arch}_prefill{tokens}_ms"] = round(timed["ms"], 3)
                 result[f"{name}_{arch}_prefill{tokens}_tokens_per_s"] = round(tokens / (timed["ms"] * 1e-3))
-            for batch in ((args.batch,) if args.only == "decode" else (1, 8, 64)):
+            for batch in {"decode": (args.batch,), "prefill": ()}.get(args.only, (1, 8, 64)):
                 timed = time_decode(runner, sampler, manager, batch, CONTEXT, args.steps, args.warmup,
                                     min_seconds=0.0 if args.only == "decode" else 0.2)
                 result[f"{name}_{arch}_decode_b{batch}_ms"] = round(timed["ms_per_step"], 3)
@@ -737,7 +737,7 @@ def run_kanavik(args) -> dict:
                 result[f"{name}_{arch}_decode_b{batch}_launches_per_step"] = timed["launches"] // max(1, args.steps)
             del runner, manager, sampler
             torch.cuda.empty_cache()
-    if args.only != "decode":
+    if args.only == "all":
         result["kernels"] = kanavik_kernels(peak)
     return result
 
@@ -765,7 +765,8 @@ def kanavik_kernels(peak: dict) -> dict:
 
     window = 1024
     for width, ff, heads, kv_heads, size in ((896, 4864, 14, 2, 64), (1536, 8960, 12, 2, 128)):
-        ops.ensure_built(list(ops.attention_libraries(size, PAGE)) + ["recurrence", "pointwise", "stream", "attention_mixed"])
+        ops.ensure_built(list(ops.attention_libraries(size, PAGE)) + ["recurrence", "pointwise", "stream", "attention_mixed",
+                                                                         "attention_mixed_tiled:" + ops.mixed_tiled_variant(heads)])
         tag = f"w{width}"
         slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], device=device)
         talk = (torch.eye(heads, device=device) + 0.1 * torch.randn(heads, heads, device=device)).contiguous()
@@ -788,7 +789,8 @@ def kanavik_kernels(peak: dict) -> dict:
         def mixed_prefill():
             table = tables[turn[0] % launches]
             turn[0] += 1
-            ops.paged_attention_mixed(q, k, v, table, seq0, pos0, o, size ** -0.5, window, slopes, talk, sink, 1.0, status)
+            ops.paged_attention_mixed(q, k, v, table, seq0, pos0, o, size ** -0.5, window, slopes, talk, sink, 1.0, status,
+                                      q_tiles=tiles, num_singles=0, max_context=tokens)
 
         def plain_prefill():
             table = tables[turn[0] % launches]
@@ -817,7 +819,7 @@ def kanavik_kernels(peak: dict) -> dict:
                 table = dtables[turn[0] % launches]
                 turn[0] += 1
                 ops.paged_attention_mixed(qd, k, v, table, seq, positions, od, size ** -0.5, window, slopes, talk, sink,
-                                          1.0, status)
+                                          1.0, status, q_tiles=tiles[:0], num_singles=batch, max_context=context)
 
             def plain_decode():
                 table = dtables[turn[0] % launches]
@@ -984,7 +986,7 @@ def run_bomipel(args) -> dict:
                 timed = time_prefill(runner, sampler, manager, tokens, repeats=5)
                 result[f"{name}_{arch}_prefill{tokens}_ms"] = round(timed["ms"], 3)
                 result[f"{name}_{arch}_prefill{tokens}_tokens_per_s"] = round(tokens / (timed["ms"] * 1e-3))
-            for batch in ((args.batch,) if args.only == "decode" else (1, 8, 64)):
+            for batch in {"decode": (args.batch,), "prefill": ()}.get(args.only, (1, 8, 64)):
                 timed = time_decode(runner, sampler, manager, batch, CONTEXT, args.steps, args.warmup,
                                     min_seconds=0.0 if args.only == "decode" else 0.2)
                 result[f"{name}_{arch}_decode_b{batch}_ms"] = round(timed["ms_per_step"], 3)

@@ -44,6 +44,7 @@ struct MixedTiledArgs {
   const float* sink;
   float out_scale;
   int rows, blocks_per_tile, splits;
+  int groups_at_once;        // key/value heads whose tiles are in shared memory together
   float* part_acc;           // [splits, tokens, heads * vdim]
   float* part_ml;            // [splits, tokens, heads, 2]
   int num_tokens;
@@ -74,8 +75,66 @@ __device__ __forceinline__ BlockPlace block_place(const MixedTiledArgs& a) {
   return b;
 }
 
+// Rows j0 .. j0 + 63 of `groups` key/value heads from g0 on, as floats: tile[(g * 64 + key) * ld + d]; rows from
+// `count` on are zeros.  `pages` holds the tile's 64 page numbers.  16-byte loads, four in flight a thread,
+// where the row width allows; a page outside the pool leaves zeros and sets the status word.
+template <typename T>
+__device__ __forceinline__ void load_tile(float* __restrict__ tile, int ld, const T* __restrict__ cache, int width,
+                                          int g0, int groups, int kv_heads, int page_size, int num_pages,
+                                          const int* __restrict__ pages, int j0, int count, int* status) {
+  constexpr int kEach = 16 / (int)sizeof(T);
+  const int tid = threadIdx.x;
+  if (width % kEach == 0) {
+    const int chunks = width / kEach, total = groups * kKeyTile * chunks;
+    for (int base = tid; base < total; base += 4 * kTiledThreads) {
+      uint4 raw[4];
+      int at[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int idx = base + e * kTiledThreads;
+        raw[e] = make_uint4(0u, 0u, 0u, 0u);
+        at[e] = -1;
+        if (idx < total) {
+          const int row = idx / chunks, c = idx - row * chunks;
+          const int g = row / kKeyTile, key = row - g * kKeyTile;
+          at[e] = row * ld + c * kEach;
+          if (key < count) {
+            const int j = j0 + key, page = pages[key];
+            if (page >= 0 && page < num_pages)
+              raw[e] = *(const uint4*)(cache + (((size_t)page * kv_heads + g0 + g) * page_size + j % page_size) * width +
+                                       c * kEach);
+            else if (c == 0) atomicOr(status, kStatusBadPage);
+          }
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (at[e] < 0) continue;
+        const T* v = (const T*)&raw[e];
+#pragma unroll
+        for (int x = 0; x < kEach; x += 4)
+          *(float4*)(tile + at[e] + x) = make_float4(to_float(v[x]), to_float(v[x + 1]), to_float(v[x + 2]), to_float(v[x + 3]));
+      }
+    }
+    return;
+  }
+  const int total = groups * kKeyTile * width;
+  for (int idx = tid; idx < total; idx += kTiledThreads) {
+    const int row = idx / width, d = idx - row * width;
+    const int g = row / kKeyTile, key = row - g * kKeyTile;
+    float value = 0.f;
+    if (key < count) {
+      const int j = j0 + key, page = pages[key];
+      if (page >= 0 && page < num_pages)
+        value = to_float(cache[(((size_t)page * kv_heads + g0 + g) * page_size + j % page_size) * width + d]);
+      else if (d == 0) atomicOr(status, kStatusBadPage);
+    }
+    tile[row * ld + d] = value;
+  }
+}
+
 template <typename T, int QI, int VD>
-__global__ void __launch_bounds__(kTiledThreads) paged_attention_mixed_tiled_kernel(const __grid_constant__ MixedTiledArgs a) {
+__global__ void __launch_bounds__(kTiledThreads, 2) paged_attention_mixed_tiled_kernel(const __grid_constant__ MixedTiledArgs a) {
   constexpr int NT = QI == 1 ? 4 : 16 / VD;           // (head, query group) tasks a warp may hold
   extern __shared__ float4 smem4[];
   float* smem = (float*)smem4;
@@ -84,13 +143,15 @@ __global__ void __launch_bounds__(kTiledThreads) paged_attention_mixed_tiled_ker
   const int nq = QB / QI;                             // query groups
   const int ldk = dim + 4;
   float* qs = smem;                                   // [heads * QB, dim], scaled
-  float* kv = qs + heads * QB * dim;                  // [64, ldk] keys, then [64, vdim] values
-  float* sc = kv + kKeyTile * max(ldk, vdim);         // [heads * QB, 64]
+  const int GB = a.groups_at_once;
+  float* kv = qs + heads * QB * dim;                  // [GB * 64, ldk] keys, then [GB * 64, vdim] values
+  float* sc = kv + GB * kKeyTile * max(ldk, vdim);    // [heads * QB, 64]
   float* talk_s = sc + heads * QB * kKeyTile;         // [heads, kHP]
   float* slope_s = talk_s + heads * kHP;              // [kHP]
   float* top = slope_s + kHP;                         // [heads * QB]
   float* total = top + heads * QB;
   float* factor = total + heads * QB;
+  int* pages = (int*)(factor + heads * QB);           // [2, 64] page numbers of this tile and the next
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -132,32 +193,31 @@ __global__ void __launch_bounds__(kTiledThreads) paged_attention_mixed_tiled_ker
 #pragma unroll
       for (int dd = 0; dd < VD; ++dd) acc[n][qi][dd] = 0.f;
 
+  if (tid < kKeyTile && tile_first < tile_last) {
+    const int j = lo + tile_first * kKeyTile + tid;
+    pages[(tile_first & 1) * kKeyTile + tid] = j <= hi ? table[j / a.page_size] : 0;
+  }
   for (int tile = tile_first; tile < tile_last; ++tile) {
     const int j0 = lo + tile * kKeyTile;
     const int count = min(kKeyTile, hi - j0 + 1);
-    // ---- raw scores, one key/value head after the other
-    for (int g = 0; g < a.kv_heads; ++g) {
-      __syncthreads();                                // kv is free (and, the first time, qs is written)
-      for (int idx = tid; idx < kKeyTile * dim; idx += kTiledThreads) {
-        const int key = idx / dim, d = idx - key * dim;
-        float value = 0.f;
-        if (key < count) {
-          const int j = j0 + key;
-          const int page = table[j / a.page_size];
-          if (page >= 0 && page < a.num_pages)
-            value = to_float(k_cache[(((size_t)page * a.kv_heads + g) * a.page_size + j % a.page_size) * dim + d]);
-          else if (d == 0) atomicOr(a.status, kStatusBadPage);
-        }
-        kv[key * ldk + d] = value;
-      }
+    const int* tile_pages = pages + (tile & 1) * kKeyTile;
+    if (tid < kKeyTile && tile + 1 < tile_last) {     // read after the barriers below, written again two tiles on
+      const int j = j0 + kKeyTile + tid;
+      pages[((tile + 1) & 1) * kKeyTile + tid] = j <= hi ? table[j / a.page_size] : 0;
+    }
+    // ---- raw scores, a few key/value heads after the others
+    for (int g0 = 0; g0 < a.kv_heads; g0 += GB) {
+      const int groups = min(GB, a.kv_heads - g0);
+      __syncthreads();                                // kv is free (and, the first time, qs and pages are written)
+      load_tile(kv, ldk, k_cache, dim, g0, groups, a.kv_heads, a.page_size, a.num_pages, tile_pages, j0, count, a.status);
       __syncthreads();
-      for (int task = warp; task < per * nq; task += kTiledWarps) {
-        const int h = g * per + task / nq, iq = task % nq;
+      for (int task = warp; task < groups * per * nq; task += kTiledWarps) {
+        const int h = g0 * per + task / nq, iq = task % nq;
         float s[QI][2];
 #pragma unroll
         for (int qi = 0; qi < QI; ++qi) s[qi][0] = s[qi][1] = 0.f;
-        const float* k0 = kv + lane * ldk;
-        const float* k1 = kv + (lane + 32) * ldk;
+        const float* k0 = kv + ((h / per - g0) * kKeyTile + lane) * ldk;
+        const float* k1 = k0 + 32 * ldk;
         const float* qr = qs + (size_t)(h * QB + iq * QI) * dim;
         for (int d = 0; d < dim; d += 4) {
           const float4 x0 = *(const float4*)(k0 + d), x1 = *(const float4*)(k1 + d);
@@ -234,26 +294,19 @@ __global__ void __launch_bounds__(kTiledThreads) paged_attention_mixed_tiled_ker
       }
     }
     // ---- values, one key/value head after the other
-    for (int g = 0; g < a.kv_heads; ++g) {
+    for (int g0 = 0; g0 < a.kv_heads; g0 += GB) {
+      const int groups = min(GB, a.kv_heads - g0);
       __syncthreads();                                // weights and factors are written; kv is free
-      for (int idx = tid; idx < kKeyTile * vdim; idx += kTiledThreads) {
-        const int key = idx / vdim, d = idx - key * vdim;
-        float value = 0.f;
-        if (key < count) {
-          const int j = j0 + key;
-          const int page = table[j / a.page_size];
-          if (page >= 0 && page < a.num_pages)
-            value = to_float(v_cache[(((size_t)page * a.kv_heads + g) * a.page_size + j % a.page_size) * vdim + d]);
-        }
-        kv[idx] = value;
-      }
+      load_tile(kv, vdim, v_cache, vdim, g0, groups, a.kv_heads, a.page_size, a.num_pages, tile_pages, j0, count, a.status);
       __syncthreads();
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
         const int task = n * kTiledWarps + warp;
         if (task >= heads * nq) continue;
         const int h = task / nq, iq = task - h * nq;
-        if (h / per != g) continue;
+        const int g = h / per - g0;
+        if (g < 0 || g >= groups) continue;
+        const float* values = kv + (size_t)g * kKeyTile * vdim;
         const int r0 = h * QB + iq * QI;
 #pragma unroll
         for (int qi = 0; qi < QI; ++qi) {
@@ -268,7 +321,7 @@ __global__ void __launch_bounds__(kTiledThreads) paged_attention_mixed_tiled_ker
 #pragma unroll
             for (int dd = 0; dd < VD; ++dd) {
               const int d = lane + 32 * dd;
-              v[e][dd] = d < vdim ? kv[(key + e) * vdim + d] : 0.f;
+              v[e][dd] = d < vdim ? values[(key + e) * vdim + d] : 0.f;
             }
 #pragma unroll
           for (int qi = 0; qi < QI; ++qi) {
@@ -345,27 +398,38 @@ __global__ void __launch_bounds__(kTiledThreads) mixed_join_kernel(const __grid_
 
 using namespace einf;
 
-static size_t tiled_bytes(int heads, int dim, int vdim, int rows) {
-  const size_t floats = (size_t)heads * rows * dim + (size_t)kKeyTile * (dim + 4 > vdim ? dim + 4 : vdim) +
-                        (size_t)heads * rows * kKeyTile + (size_t)heads * kHP + kHP + 3 * (size_t)heads * rows;
+static size_t tiled_bytes(int heads, int dim, int vdim, int rows, int groups) {
+  const size_t floats = (size_t)heads * rows * dim + (size_t)groups * kKeyTile * (dim + 4 > vdim ? dim + 4 : vdim) +
+                        (size_t)heads * rows * kKeyTile + (size_t)heads * kHP + kHP + 3 * (size_t)heads * rows +
+                        2 * kKeyTile;
   return floats * sizeof(float);
 }
 
-// Rows a CTA takes for tasks of four queries: the most of 16, 8, 4 whose tasks fit a warp's registers and
-// whose shared memory leaves room for two CTAs an SM, else the most that fits at all; 0: none does.
-static int tiled_rows(int heads, int dim, int vdim) {
+struct TiledShape {
+  int rows, groups;
+};
+
+// Queries a CTA takes and key/value heads it holds at once.  Tasks of four queries: the most rows of 16, 8, 4
+// whose tasks fit a warp's registers, with all key/value heads at once or else one, that leaves room for two
+// CTAs an SM; else the most that fits at all.  rows 0: none does.
+static TiledShape tiled_shape(int heads, int kv_heads, int dim, int vdim, int single) {
+  const size_t limits[2] = {(size_t)112 * 1024, (size_t)220 * 1024};
   const int value_lanes = (vdim + 31) / 32;
   const int tasks = kTiledWarps * (16 / (value_lanes <= 1 ? 1 : value_lanes <= 2 ? 2 : 4));
-  for (size_t limit : {(size_t)100 * 1024, (size_t)220 * 1024})
-    for (int rows : {16, 8, 4})
-      if (heads * (rows / 4) <= tasks && tiled_bytes(heads, dim, vdim, rows) <= limit) return rows;
-  return 0;
+  for (size_t limit : limits)
+    for (int rows : {16, 8, 4}) {
+      if (single) rows = 1;
+      for (int groups : {kv_heads, 1})
+        if ((single || heads * (rows / 4) <= tasks) && tiled_bytes(heads, dim, vdim, rows, groups) <= limit)
+          return {rows, groups};
+    }
+  return {0, 0};
 }
 
 template <typename T, int QI, int VD>
 static int launch_tiled(const MixedTiledArgs& a, int blocks, cudaStream_t stream) {
   auto kernel = paged_attention_mixed_tiled_kernel<T, QI, VD>;
-  const size_t bytes = tiled_bytes(a.heads, a.dim, a.vdim, a.rows);
+  const size_t bytes = tiled_bytes(a.heads, a.dim, a.vdim, a.rows, a.groups_at_once);
   if (bytes > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return (int)e;
@@ -376,10 +440,10 @@ static int launch_tiled(const MixedTiledArgs& a, int blocks, cudaStream_t stream
 }
 
 // Rows per CTA for the given sizes (0: this kernel does not take them; 1 with `single`).
-extern "C" int einf_paged_attention_mixed_tiled_rows(int heads, int dim, int vdim, int single) {
-  if (heads <= 0 || heads > kHP || dim <= 0 || dim % 4 || vdim <= 0 || vdim > 128) return 0;
-  if (single) return tiled_bytes(heads, dim, vdim, 1) <= (size_t)220 * 1024 ? 1 : 0;
-  return tiled_rows(heads, dim, vdim);
+extern "C" int einf_paged_attention_mixed_tiled_rows(int heads, int kv_heads, int dim, int vdim, int single) {
+  if (heads <= 0 || heads > kHP || kv_heads <= 0 || heads % kv_heads || dim <= 0 || dim % 4 || vdim <= 0 || vdim > 128)
+    return 0;
+  return tiled_shape(heads, kv_heads, dim, vdim, single).rows;
 }
 
 // `items`: q_tiles [num_items, 4] with single == 0; token indices [num_items] (or null: tokens 0 .. num_items - 1)
@@ -393,8 +457,8 @@ extern "C" int einf_paged_attention_mixed_tiled(const void* q, const void* k_cac
                                                 float out_scale, int splits, float* part_acc, float* part_ml,
                                                 int* status, cudaStream_t stream) {
   if (num_items == 0) return 0;
-  const int rows = einf_paged_attention_mixed_tiled_rows(heads, dim, vdim, single);
-  if (rows == 0 || kv_heads <= 0 || heads % kv_heads || splits < 1 || splits > 65535 ||
+  const int rows = einf_paged_attention_mixed_tiled_rows(heads, kv_heads, dim, vdim, single);
+  if (rows == 0 || splits < 1 || splits > 65535 ||
       (splits > 1 && (!part_acc || !part_ml)))
     return (int)cudaErrorInvalidValue;
   MixedTiledArgs a;
@@ -403,6 +467,7 @@ extern "C" int einf_paged_attention_mixed_tiled(const void* q, const void* k_cac
   a.q_tiles = single ? nullptr : items; a.single_tokens = single ? items : nullptr;
   a.out = out; a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.page_size = page_size;
   a.num_pages = num_pages; a.scale = scale; a.window = window; a.slopes = slopes; a.talk = talk; a.sink = sink;
+  a.groups_at_once = tiled_shape(heads, kv_heads, dim, vdim, single).groups;
   a.out_scale = out_scale; a.rows = rows; a.blocks_per_tile = single ? 1 : (128 + rows - 1) / rows; a.splits = splits;
   a.part_acc = part_acc; a.part_ml = part_ml; a.num_tokens = num_tokens; a.status = status;
   const int blocks = num_items * a.blocks_per_tile;

@@ -7,6 +7,8 @@
 // (float or bfloat16) or the float partial sums [S, T, H] of a split-K product, and are added in
 // a fixed order: term a split by split, then term b, then scaled, then added to the row.  Every
 // row is computed by one CTA from the row's own request alone.
+#include <cstdint>
+
 #include "common.cuh"
 
 namespace einf {
@@ -256,6 +258,181 @@ __global__ void stream_tail_kernel(float* __restrict__ residual, const __grid_co
   }
 }
 
+// The same end of a layer for TB tokens a CTA, so the two token-input matrices are read once for all of them,
+// in 16-byte pieces (hidden a multiple of 8).  s = gate x: a warp per pair of rows of gate, its lanes over the
+// row's pieces, the tokens' x from shared memory.  y = proj_t^T g: a warp per eight pieces of columns, four
+// lanes per piece that share the rows of proj_t and add up by shuffles in a fixed order.
+constexpr int kTailThreads = 512;
+
+template <typename TW>
+__device__ __forceinline__ void piece_to_floats(const uint4& raw, float (&w)[8]);
+template <>
+__device__ __forceinline__ void piece_to_floats<__nv_bfloat16>(const uint4& raw, float (&w)[8]) {
+  const __nv_bfloat162* p = (const __nv_bfloat162*)&raw;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(p[e]);
+    w[2 * e] = f.x;
+    w[2 * e + 1] = f.y;
+  }
+}
+
+// eight weights of row `row` from column c on
+template <typename TW>
+__device__ __forceinline__ void load_piece(const TW* __restrict__ m, size_t at, float (&w)[8]) {
+  if (sizeof(TW) == 2) {
+    const uint4 raw = *(const uint4*)(m + at);
+    piece_to_floats<__nv_bfloat16>(raw, w);
+  } else {
+    const float4 lo = *(const float4*)((const float*)m + at), hi = *(const float4*)((const float*)m + at + 4);
+    w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w; w[4] = hi.x; w[5] = hi.y; w[6] = hi.z; w[7] = hi.w;
+  }
+}
+
+template <typename TW, int TB>
+__global__ void __launch_bounds__(kTailThreads)
+stream_tail_tokens_kernel(float* __restrict__ residual, const __grid_constant__ Pending pending, float scale,
+                          const int* __restrict__ token_ids, const TW* __restrict__ table, const TW* __restrict__ gate,
+                          const TW* __restrict__ proj_t, const float* __restrict__ norm, int side, int vocab, float eps,
+                          float* __restrict__ history, int depth_index, const float* __restrict__ depth_weight,
+                          long long history_stride, int hidden, int num_tokens) {
+  extern __shared__ float4 smem4[];
+  float* x = (float*)smem4;          // [TB, hidden]
+  float* y = x + TB * hidden;        // [TB, hidden]
+  float* g = y + TB * hidden;        // [TB, side]
+  float* red = g + TB * side;        // [TB, warps]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kWarps = kTailThreads / 32;
+  const int t0 = blockIdx.x * TB;
+  const int count = min(TB, num_tokens - t0);
+  const bool adds = pending.a != nullptr || pending.b != nullptr;
+  for (int idx = tid; idx < TB * hidden; idx += kTailThreads) {
+    const int i = idx / hidden;
+    float v = 0.f;
+    if (i < count) {
+      const size_t at = (size_t)t0 * hidden + idx;
+      v = residual[at];
+      if (adds) v += scale * pending_sum(pending, at);
+    }
+    x[idx] = v;
+  }
+  __syncthreads();
+  if (table) {
+    const int pieces = hidden / 8;
+    // s = gate x, two rows a warp at a time
+    for (int d0 = 2 * warp; d0 < side; d0 += 2 * kWarps) {
+      float dot[2][TB];
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int i = 0; i < TB; ++i) dot[r][i] = 0.f;
+      for (int p = lane; p < pieces; p += 32) {
+        float w[2][8];
+        load_piece<TW>(gate, (size_t)d0 * hidden + 8 * p, w[0]);
+        if (d0 + 1 < side) load_piece<TW>(gate, (size_t)(d0 + 1) * hidden + 8 * p, w[1]);
+#pragma unroll
+        for (int i = 0; i < TB; ++i) {
+          const float4 a = *(const float4*)(x + i * hidden + 8 * p), b = *(const float4*)(x + i * hidden + 8 * p + 4);
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            float acc = dot[r][i];
+            acc = fmaf(w[r][0], a.x, acc); acc = fmaf(w[r][1], a.y, acc); acc = fmaf(w[r][2], a.z, acc);
+            acc = fmaf(w[r][3], a.w, acc); acc = fmaf(w[r][4], b.x, acc); acc = fmaf(w[r][5], b.y, acc);
+            acc = fmaf(w[r][6], b.z, acc); acc = fmaf(w[r][7], b.w, acc);
+            dot[r][i] = acc;
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int i = 0; i < TB; ++i) {
+          const float total = warp_sum(dot[r][i]);
+          if (lane == 0 && d0 + r < side && i < count) {
+            int token = token_ids[t0 + i];
+            token = token < 0 ? 0 : (token >= vocab ? vocab - 1 : token);     // a bad id was reported by the embedding
+            g[i * side + d0 + r] = gelu_tanh_f(total) * to_float(table[(size_t)token * side + d0 + r]);
+          }
+        }
+    }
+    __syncthreads();
+    // y = proj_t^T g
+    float ss[TB];
+#pragma unroll
+    for (int i = 0; i < TB; ++i) ss[i] = 0.f;
+    const int part = lane >> 3;                       // which quarter of the rows of proj_t
+    for (int p = 8 * warp + (lane & 7); p - (lane & 7) < pieces; p += 8 * kWarps) {
+      float acc[TB][8];
+#pragma unroll
+      for (int i = 0; i < TB; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+      if (p < pieces) {
+#pragma unroll 4
+        for (int d = part; d < side; d += 4) {
+          float w[8];
+          load_piece<TW>(proj_t, (size_t)d * hidden + 8 * p, w);
+#pragma unroll
+          for (int i = 0; i < TB; ++i) {
+            const float gi = g[i * side + d];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[i][e] = fmaf(w[e], gi, acc[i][e]);
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < TB; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float v = acc[i][e];
+          v += __shfl_xor_sync(0xffffffffu, v, 8);
+          v += __shfl_xor_sync(0xffffffffu, v, 16);
+          acc[i][e] = v;
+        }
+      if (part == 0 && p < pieces) {
+#pragma unroll
+        for (int i = 0; i < TB; ++i) {
+          if (i >= count) continue;
+          *(float4*)(y + i * hidden + 8 * p) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+          *(float4*)(y + i * hidden + 8 * p + 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ss[i] = fmaf(acc[i][e], acc[i][e], ss[i]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < TB; ++i) {
+      const float total = warp_sum(ss[i]);
+      if (lane == 0) red[i * kWarps + warp] = total;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < count * hidden; idx += kTailThreads) {
+      const int i = idx / hidden, c = idx - i * hidden;
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) total += red[i * kWarps + w];
+      const float inv = rsqrtf(total / (float)hidden + eps);
+      x[idx] = fmaf(scale * inv * norm[c], y[idx], x[idx]);
+    }
+    // every thread reads back the elements it wrote itself: no barrier is needed before the next loop
+  }
+  if (history) {
+    const float newest = depth_weight[depth_index + 1];
+    for (int idx = tid; idx < count * hidden; idx += kTailThreads) {
+      const size_t at = (size_t)t0 * hidden + idx;
+      const float v = x[idx];
+      history[(size_t)(depth_index + 1) * history_stride + at] = v;
+      float acc = 0.f;
+      for (int j = 0; j <= depth_index; ++j) acc = fmaf(depth_weight[j], history[(size_t)j * history_stride + at], acc);
+      residual[at] = fmaf(newest, v, acc);
+    }
+  } else {
+    for (int idx = tid; idx < count * hidden; idx += kTailThreads) residual[(size_t)t0 * hidden + idx] = x[idx];
+  }
+}
+
 static int row_threads(int hidden) {
   int threads = 64;
   while (threads < hidden / 4 && threads < 512) threads <<= 1;
@@ -311,6 +488,28 @@ extern "C" int einf_stream_tail(float* residual, const void* pend_a, int a_dtype
   if (num_tokens == 0) return 0;
   if (hidden <= 0 || side < 0) return (int)cudaErrorInvalidValue;
   const Pending pending{pend_a, a_dtype, a_splits, a_stride, pend_b, b_dtype, b_splits, b_stride};
+  if (hidden % 8 == 0 && side > 0 && ((uintptr_t)gate | (uintptr_t)proj_t) % 16 == 0) {
+    // several tokens a CTA: eight for a long step where they fit beside a second CTA, else four
+    auto bytes = [&](int each) { return (size_t)(2 * each * hidden + each * side + each * (kTailThreads / 32)) * sizeof(float); };
+    const int each = (num_tokens >= 1024 && bytes(8) <= 100 * 1024) ? 8 : 4;
+    if (bytes(each) <= 200 * 1024) {
+      const int blocks = (num_tokens + each - 1) / each;
+#define EINF_TAIL(TB)                                                                                                   \
+  EINF_DISPATCH_2(weight_dtype, T, {                                                                                    \
+    auto kernel = stream_tail_tokens_kernel<T, TB>;                                                                     \
+    if (bytes(TB) > 48 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes(TB));        \
+      if (e != cudaSuccess) return (int)e;                                                                              \
+    }                                                                                                                   \
+    return (int)launch_pdl(kernel, blocks, kTailThreads, bytes(TB), stream, residual, pending, scale, token_ids,       \
+                           (const T*)table, (const T*)gate, (const T*)proj_t, norm, side, vocab, eps, history,          \
+                           depth_index, depth_weight, history_stride, hidden, num_tokens);                              \
+  })
+      if (each == 8) EINF_TAIL(8)
+      EINF_TAIL(4)
+#undef EINF_TAIL
+    }
+  }
   const int threads = row_threads(hidden);
   const size_t smem = (size_t)(2 * hidden + side + 33) * sizeof(float);
   EINF_DISPATCH_2(weight_dtype, T, {

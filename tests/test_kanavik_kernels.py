@@ -69,7 +69,7 @@ def test_tiled_score_mixing_attention(dev, dtype, heads, kv_heads, size, vsize, 
         extra = dict(q_tiles=q_tiles.to(dev), single_tokens=singles.to(dev), num_singles=singles.shape[0],
                      max_context=max(s + n for s, n in requests)) if tiled else {}
         if tiled:
-            assert ops.mixed_tiled_rows(heads, size, vsize, False) and ops.mixed_tiled_rows(heads, size, vsize, True)
+            assert ops.mixed_tiled_rows(heads, kv_heads, size, vsize, False) and ops.mixed_tiled_rows(heads, kv_heads, size, vsize, True)
         ops.paged_attention_mixed(q, k, v, table, seq, pos, out, scale, window, slopes, talk, sink, 0.7, st, **extra)
         assert int(st) == 0
         torch.testing.assert_close(out.cpu(), want_cpu, **close)
@@ -158,3 +158,42 @@ def test_gated_scan_in_segments(dev, dtype, lengths):
     close = dict(rtol=2e-4, atol=2e-5) if dtype == torch.float32 else tol(dtype)
     torch.testing.assert_close(got.cpu(), want, **close)
     torch.testing.assert_close(got_state.cpu(), want_state, rtol=2e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens, hidden, side, layers_done", [
+    (1, 64, 8, 0), (5, 72, 6, 2), (9, 100, 16, 1), (1030, 128, 64, 3), (8, 896, 64, 7), (3, 1544, 33, 0),
+])
+@pytest.mark.parametrize("parts", ["both", "token input", "depth average", "neither"])
+def test_end_of_a_layer(dev, dtype, tokens, hidden, side, layers_done, parts):
+    """The kernel that takes several tokens a CTA (widths that are multiples of eight) and the one that
+    takes a row a CTA (the others): pending sublayer output, token input, depth average."""
+    from einf_b200 import ops
+
+    if parts != "both" and tokens not in (5, 1030):
+        pytest.skip("the parts alone at two sizes")
+    generator = torch.Generator().manual_seed(tokens + hidden)
+    vocab = 50
+    residual = torch.randn((tokens, hidden), generator=generator)
+    pending = [torch.randn((tokens, hidden), generator=generator).to(dtype)]
+    ids = torch.randint(0, vocab, (tokens,), generator=generator, dtype=torch.int32)
+    table = torch.randn((vocab, side), generator=generator).to(dtype)
+    gate = (torch.randn((side, hidden), generator=generator) * hidden ** -0.5).to(dtype)
+    proj_t = torch.randn((side, hidden), generator=generator).to(dtype)
+    norm = torch.rand((hidden,), generator=generator) + 0.5
+    history = torch.randn((layers_done + 2, tokens, hidden), generator=generator)
+    weight = torch.randn((layers_done + 2,), generator=generator)
+    use_side, use_depth = parts in ("both", "token input"), parts in ("both", "depth average")
+
+    def arguments(move):
+        return (move(residual.clone()), [move(t) for t in pending], 0.6, move(ids),
+                (move(table), move(gate), move(proj_t), move(norm), 1e-5) if use_side else None,
+                (move(history.clone()), layers_done, move(weight)) if use_depth else None)
+
+    want, got = arguments(lambda t: t), arguments(lambda t: t.to(dev))
+    ref.stream_tail(*want)
+    ops.stream_tail(*got)
+    close = dict(rtol=2e-4, atol=2e-4) if dtype == torch.float32 else dict(rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(got[0].cpu(), want[0], **close)
+    if use_depth:
+        torch.testing.assert_close(got[5][0].cpu(), want[5][0], **close)
