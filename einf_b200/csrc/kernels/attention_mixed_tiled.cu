@@ -367,6 +367,291 @@ __global__ void __launch_bounds__(kTiledThreads, 2) paged_attention_mixed_tiled_
   }
 }
 
+#if HEADS_PAD <= 16
+// ---------------------------------------------------------------------------
+// The same for bfloat16 prompt portions with the two products on the tensor cores (mma.sync m16n8k16, 32-bit
+// accumulators): 16 queries a CTA.  Queries, keys and values sit in shared memory as they are stored.  Raw
+// scores: warp w takes keys 8w .. 8w + 7 of the tile for all heads, so a thread holds every head's score at
+// its four (query, key) places and scales, takes the distance off and mixes in registers; the mixed scores go
+// to shared memory as floats.  A warp per (head, query) row then updates maximum and sum and leaves each
+// weight in the row's place as two bfloat16 terms (w = hi + lo, 16 bits of mantissa), and the weighted values
+// are two products per (head, 32 value columns) task.
+// ---------------------------------------------------------------------------
+constexpr int kMmaRows = 16;
+constexpr int kScoreStride = kKeyTile + 4;            // floats; rows 16 bytes apart in the banks
+
+__device__ __forceinline__ void ldmatrix4(uint32_t (&r)[4], const void* p) {
+  const uint32_t at = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(at));
+}
+__device__ __forceinline__ void ldmatrix4_transposed(uint32_t (&r)[4], const void* p) {
+  const uint32_t at = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(at));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&x)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]), "r"(b0), "r"(b1));
+}
+
+// rows j0 .. j0 + 63 of every key/value head as stored: tile[(g * 64 + key) * ld + d]; zeros from `count` on
+__device__ __forceinline__ void load_tile_bf16(__nv_bfloat16* __restrict__ tile, int ld, const __nv_bfloat16* __restrict__ cache,
+                                               int width, int kv_heads, int page_size, int num_pages,
+                                               const int* __restrict__ pages, int j0, int count, int* status) {
+  const int chunks = width / 8, total = kv_heads * kKeyTile * chunks;
+  for (int base = threadIdx.x; base < total; base += 4 * kTiledThreads) {
+    uint4 raw[4];
+    int at[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = base + e * kTiledThreads;
+      raw[e] = make_uint4(0u, 0u, 0u, 0u);
+      at[e] = -1;
+      if (idx < total) {
+        const int row = idx / chunks, c = idx - row * chunks;
+        const int g = row / kKeyTile, key = row - g * kKeyTile;
+        at[e] = row * ld + c * 8;
+        if (key < count) {
+          const int j = j0 + key, page = pages[key];
+          if (page >= 0 && page < num_pages)
+            raw[e] = *(const uint4*)(cache + (((size_t)page * kv_heads + g) * page_size + j % page_size) * width + c * 8);
+          else if (c == 0) atomicOr(status, kStatusBadPage);
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (at[e] >= 0) *(uint4*)(tile + at[e]) = raw[e];
+  }
+}
+
+template <int VB>
+__global__ void __launch_bounds__(kTiledThreads, 1) paged_attention_mixed_mma_kernel(const __grid_constant__ MixedTiledArgs a) {
+  constexpr int NT = (kHP * VB + kTiledWarps - 1) / kTiledWarps;      // (head, 32 value columns) tasks a warp may hold
+  extern __shared__ float4 smem4[];
+  const int heads = a.heads, dim = a.dim, vdim = a.vdim, kv_heads = a.kv_heads;
+  const int per = heads / kv_heads;
+  const int ldq = dim + 8, ldv = vdim + 8;
+  __nv_bfloat16* qs = (__nv_bfloat16*)smem4;                          // [heads * 16, ldq]
+  __nv_bfloat16* ks = qs + heads * kMmaRows * ldq;                    // [kv_heads * 64, ldq]
+  __nv_bfloat16* vs = ks + kv_heads * kKeyTile * ldq;                 // [kv_heads * 64, ldv]
+  float* sc = (float*)(vs + kv_heads * kKeyTile * ldv);               // [heads * 16, kScoreStride]
+  float* talk_s = sc + heads * kMmaRows * kScoreStride;               // [heads, kHP]
+  float* slope_s = talk_s + heads * kHP;                              // [kHP]
+  float* top = slope_s + kHP;                                         // [heads * 16]
+  float* total = top + heads * kMmaRows;
+  float* factor = total + heads * kMmaRows;
+  int* pages = (int*)(factor + heads * kMmaRows);                     // [2, 64]
+
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gl = lane >> 2, tl = lane & 3;                            // the thread's row and column pair in a fragment
+  const int mrow = (lane & 7) + ((lane >> 3) & 1) * 8, mcol = (lane >> 4) * 8;   // its row address for ldmatrix
+  const __nv_bfloat16* q = (const __nv_bfloat16*)a.q;
+  const bool joins = a.splits > 1;
+  for (int i = tid; i < heads * kHP; i += kTiledThreads) {
+    const int h = i / kHP, g = i - h * kHP;
+    talk_s[i] = g < heads ? (a.talk ? a.talk[h * heads + g] : (h == g ? 1.f : 0.f)) : 0.f;
+  }
+  for (int g = tid; g < kHP; g += kTiledThreads) slope_s[g] = (a.slopes && g < heads) ? a.slopes[g] : 0.f;
+  for (int r = tid; r < heads * kMmaRows; r += kTiledThreads) {
+    const bool with_sink = a.sink && !joins;
+    top[r] = with_sink ? a.sink[r / kMmaRows] : -INFINITY;
+    total[r] = with_sink ? 1.f : 0.f;
+  }
+  pdl_wait();
+  const BlockPlace place = block_place<4>(a);
+  if (place.rows <= 0) return;
+  const int rows = place.rows, p0 = place.first_position;
+  {
+    const int chunks = dim / 8;
+    for (int idx = tid; idx < heads * kMmaRows * chunks; idx += kTiledThreads) {
+      const int r = idx / chunks, c = idx - r * chunks;
+      const int h = r / kMmaRows, i = r - h * kMmaRows;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (i < rows) raw = *(const uint4*)(q + ((size_t)(place.first_token + i) * heads + h) * dim + c * 8);
+      *(uint4*)(qs + r * ldq + c * 8) = raw;
+    }
+  }
+  const int hi = p0 + rows - 1;
+  const int lo = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
+  const int tiles_total = (hi - lo + kKeyTile) / kKeyTile;
+  const int tiles_each = (tiles_total + a.splits - 1) / a.splits;
+  const int tile_first = blockIdx.y * tiles_each, tile_last = min(tiles_total, tile_first + tiles_each);
+  const int* table = a.block_table + (size_t)place.request * a.table_width;
+
+  float acc[NT][4][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[n][b][e] = 0.f;
+
+  if (tid < kKeyTile && tile_first < tile_last) {
+    const int j = lo + tile_first * kKeyTile + tid;
+    pages[(tile_first & 1) * kKeyTile + tid] = j <= hi ? table[j / a.page_size] : 0;
+  }
+  for (int tile = tile_first; tile < tile_last; ++tile) {
+    const int j0 = lo + tile * kKeyTile;
+    const int count = min(kKeyTile, hi - j0 + 1);
+    const int* tile_pages = pages + (tile & 1) * kKeyTile;
+    if (tid < kKeyTile && tile + 1 < tile_last) {
+      const int j = j0 + kKeyTile + tid;
+      pages[((tile + 1) & 1) * kKeyTile + tid] = j <= hi ? table[j / a.page_size] : 0;
+    }
+    __syncthreads();                                  // the tile before is used up; qs and pages are written
+    load_tile_bf16(ks, ldq, (const __nv_bfloat16*)a.k_cache, dim, kv_heads, a.page_size, a.num_pages, tile_pages, j0, count, a.status);
+    load_tile_bf16(vs, ldv, (const __nv_bfloat16*)a.v_cache, vdim, kv_heads, a.page_size, a.num_pages, tile_pages, j0, count, a.status);
+    __syncthreads();
+    {
+      // ---- raw scores of keys 8 warp .. 8 warp + 7 for every head, then distance, mixing and mask in registers
+      float s[kHP][4];
+      const int n0 = warp * 8;
+#pragma unroll
+      for (int h = 0; h < kHP; ++h) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[h][e] = 0.f;
+        if (h < heads) {
+          const __nv_bfloat16* krow = ks + ((h / per) * kKeyTile + n0 + gl) * ldq + tl * 2;
+          const __nv_bfloat16* qrow = qs + (h * kMmaRows + mrow) * ldq + mcol;
+          for (int d = 0; d < dim; d += 16) {
+            uint32_t x[4];
+            ldmatrix4(x, qrow + d);
+            mma_bf16(s[h], x, *(const uint32_t*)(krow + d), *(const uint32_t*)(krow + d + 8));
+          }
+        }
+      }
+      const int key0 = j0 + n0 + tl * 2;
+      const int pos0 = p0 + gl, pos1 = p0 + gl + 8;
+      const int reach0 = a.window > 0 ? pos0 - a.window : -1, reach1 = a.window > 0 ? pos1 - a.window : -1;
+      bool see[4];
+      see[0] = gl < rows && key0 <= pos0 && key0 > reach0;
+      see[1] = gl < rows && key0 + 1 <= pos0 && key0 + 1 > reach0;
+      see[2] = gl + 8 < rows && key0 <= pos1 && key0 > reach1;
+      see[3] = gl + 8 < rows && key0 + 1 <= pos1 && key0 + 1 > reach1;
+#pragma unroll
+      for (int h = 0; h < kHP; ++h) {
+        const float slope = slope_s[h];
+        s[h][0] = s[h][0] * a.scale - slope * (float)(pos0 - key0);
+        s[h][1] = s[h][1] * a.scale - slope * (float)(pos0 - key0 - 1);
+        s[h][2] = s[h][2] * a.scale - slope * (float)(pos1 - key0);
+        s[h][3] = s[h][3] * a.scale - slope * (float)(pos1 - key0 - 1);
+      }
+      for (int h = 0; h < heads; ++h) {
+        const float4* mix = (const float4*)(talk_s + h * kHP);
+        float m[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int g4 = 0; g4 < kHP / 4; ++g4) {
+          const float4 w = mix[g4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            m[e] = fmaf(w.x, s[4 * g4][e], m[e]); m[e] = fmaf(w.y, s[4 * g4 + 1][e], m[e]);
+            m[e] = fmaf(w.z, s[4 * g4 + 2][e], m[e]); m[e] = fmaf(w.w, s[4 * g4 + 3][e], m[e]);
+          }
+        }
+        float* row0 = sc + (size_t)(h * kMmaRows + gl) * kScoreStride + n0 + tl * 2;
+        *(float2*)row0 = make_float2(see[0] ? m[0] : -INFINITY, see[1] ? m[1] : -INFINITY);
+        *(float2*)(row0 + 8 * kScoreStride) = make_float2(see[2] ? m[2] : -INFINITY, see[3] ? m[3] : -INFINITY);
+      }
+    }
+    __syncthreads();
+    // ---- running maximum and sum, a warp per (head, query) row; each weight stays as two bfloat16 terms
+    for (int r = warp; r < heads * kMmaRows; r += kTiledWarps) {
+      float* row = sc + (size_t)r * kScoreStride;
+      const float2 v = *(const float2*)(row + 2 * lane);
+      const float best = warp_max(fmaxf(v.x, v.y));
+      const float before = top[r];
+      const float now = fmaxf(before, best);
+      const float w0 = v.x == -INFINITY ? 0.f : expf(v.x - now);
+      const float w1 = v.y == -INFINITY ? 0.f : expf(v.y - now);
+      const float sum = warp_sum(w0 + w1);
+      const __nv_bfloat16 h0 = __float2bfloat16_rn(w0), h1 = __float2bfloat16_rn(w1);
+      const __nv_bfloat16 l0 = __float2bfloat16_rn(w0 - __bfloat162float(h0)), l1 = __float2bfloat16_rn(w1 - __bfloat162float(h1));
+      __syncwarp();
+      __nv_bfloat162* terms = (__nv_bfloat162*)row;
+      terms[lane] = __halves2bfloat162(h0, h1);
+      terms[32 + lane] = __halves2bfloat162(l0, l1);
+      if (lane == 0) {
+        const float f = before == -INFINITY ? 0.f : expf(before - now);
+        factor[r] = f;
+        total[r] = fmaf(total[r], f, sum);
+        top[r] = now;
+      }
+    }
+    __syncthreads();
+    // ---- weighted values
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const int task = n * kTiledWarps + warp;
+      if (task >= heads * VB) continue;
+      const int h = task / VB, vb = task - h * VB;
+      const float f0 = factor[h * kMmaRows + gl], f1 = factor[h * kMmaRows + gl + 8];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        acc[n][b][0] *= f0; acc[n][b][1] *= f0; acc[n][b][2] *= f1; acc[n][b][3] *= f1;
+      }
+      const __nv_bfloat16* weights = (const __nv_bfloat16*)(sc + (size_t)(h * kMmaRows + mrow) * kScoreStride) + mcol;
+      const __nv_bfloat16* values = vs + ((h / per) * kKeyTile + mrow) * ldv + vb * 32 + mcol;
+#pragma unroll
+      for (int k0 = 0; k0 < kKeyTile; k0 += 16) {
+        uint32_t whi[4], wlo[4];
+        ldmatrix4(whi, weights + k0);
+        ldmatrix4(wlo, weights + kKeyTile + k0);
+#pragma unroll
+        for (int pair = 0; pair < 2; ++pair) {
+          const int col = vb * 32 + pair * 16;
+          if (col >= vdim) continue;
+          uint32_t y[4];
+          ldmatrix4_transposed(y, values + (size_t)k0 * ldv + pair * 16);
+          mma_bf16(acc[n][2 * pair], whi, y[0], y[1]);
+          mma_bf16(acc[n][2 * pair], wlo, y[0], y[1]);
+          if (col + 8 < vdim) {
+            mma_bf16(acc[n][2 * pair + 1], whi, y[2], y[3]);
+            mma_bf16(acc[n][2 * pair + 1], wlo, y[2], y[3]);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int outs = heads * vdim;
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    const int task = n * kTiledWarps + warp;
+    if (task >= heads * VB) continue;
+    const int h = task / VB, vb = task - h * VB;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int i = gl + 8 * half;
+      if (i >= rows) continue;
+      const int r = h * kMmaRows + i;
+      const size_t t = (size_t)place.first_token + i;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int d = vb * 32 + b * 8 + tl * 2;
+        if (d >= vdim) continue;
+        const float o0 = acc[n][b][2 * half], o1 = acc[n][b][2 * half + 1];
+        if (joins) {
+          *(float2*)(a.part_acc + ((size_t)blockIdx.y * a.num_tokens + t) * outs + h * vdim + d) = make_float2(o0, o1);
+        } else {
+          const float inv = a.out_scale / total[r];
+          *(__nv_bfloat162*)((__nv_bfloat16*)a.out + t * outs + h * vdim + d) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
+        }
+      }
+      if (joins && vb == 0 && tl == 0) {
+        float* ml = a.part_ml + (((size_t)blockIdx.y * a.num_tokens + t) * heads + h) * 2;
+        ml[0] = top[r];
+        ml[1] = total[r];
+      }
+    }
+  }
+}
+#endif  // HEADS_PAD <= 16
+
 // out[t, h, :] = out_scale * sum_s acc_s exp(m_s - M) / (exp(sink_h - M) + sum_s l_s exp(m_s - M)) with M the
 // largest of the splits' maxima and the sink, splits in order.  The same blocks as the kernel above.
 template <typename T, int QI>
@@ -426,6 +711,32 @@ static TiledShape tiled_shape(int heads, int kv_heads, int dim, int vdim, int si
   return {0, 0};
 }
 
+static size_t mma_bytes(int heads, int kv_heads, int dim, int vdim) {
+  return (size_t)(heads * 16 * (dim + 8) + kv_heads * kKeyTile * (dim + 8) + kv_heads * kKeyTile * (vdim + 8)) * 2 +
+         (size_t)(heads * 16 * (kKeyTile + 4) + heads * kHP + kHP + 3 * heads * 16 + 2 * kKeyTile) * sizeof(float);
+}
+
+// The tensor-core kernel takes bfloat16 prompt portions of up to 16 heads whose sizes fit its fragments.
+static bool mma_takes(int dtype, int heads, int kv_heads, int dim, int vdim) {
+  return kHP <= 16 && dtype == kBFloat16 && dim % 16 == 0 && vdim % 8 == 0 && vdim <= 128 &&
+         mma_bytes(heads, kv_heads, dim, vdim) <= (size_t)220 * 1024;
+}
+
+#if HEADS_PAD <= 16
+template <int VB>
+static int launch_mma(const MixedTiledArgs& a, int blocks, cudaStream_t stream) {
+  auto kernel = paged_attention_mixed_mma_kernel<VB>;
+  const size_t bytes = mma_bytes(a.heads, a.kv_heads, a.dim, a.vdim);
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return (int)e;
+  }
+  cudaError_t e = launch_pdl(kernel, dim3(blocks, a.splits), kTiledThreads, bytes, stream, a);
+  if (e != cudaSuccess || a.splits == 1) return (int)e;
+  return (int)launch_pdl(mixed_join_kernel<__nv_bfloat16, 4>, blocks, kTiledThreads, 0, stream, a);
+}
+#endif
+
 template <typename T, int QI, int VD>
 static int launch_tiled(const MixedTiledArgs& a, int blocks, cudaStream_t stream) {
   auto kernel = paged_attention_mixed_tiled_kernel<T, QI, VD>;
@@ -440,9 +751,10 @@ static int launch_tiled(const MixedTiledArgs& a, int blocks, cudaStream_t stream
 }
 
 // Rows per CTA for the given sizes (0: this kernel does not take them; 1 with `single`).
-extern "C" int einf_paged_attention_mixed_tiled_rows(int heads, int kv_heads, int dim, int vdim, int single) {
+extern "C" int einf_paged_attention_mixed_tiled_rows(int heads, int kv_heads, int dim, int vdim, int single, int dtype) {
   if (heads <= 0 || heads > kHP || kv_heads <= 0 || heads % kv_heads || dim <= 0 || dim % 4 || vdim <= 0 || vdim > 128)
     return 0;
+  if (!single && mma_takes(dtype, heads, kv_heads, dim, vdim)) return 16;
   return tiled_shape(heads, kv_heads, dim, vdim, single).rows;
 }
 
@@ -457,7 +769,7 @@ extern "C" int einf_paged_attention_mixed_tiled(const void* q, const void* k_cac
                                                 float out_scale, int splits, float* part_acc, float* part_ml,
                                                 int* status, cudaStream_t stream) {
   if (num_items == 0) return 0;
-  const int rows = einf_paged_attention_mixed_tiled_rows(heads, kv_heads, dim, vdim, single);
+  const int rows = einf_paged_attention_mixed_tiled_rows(heads, kv_heads, dim, vdim, single, dtype);
   if (rows == 0 || splits < 1 || splits > 65535 ||
       (splits > 1 && (!part_acc || !part_ml)))
     return (int)cudaErrorInvalidValue;
@@ -472,6 +784,14 @@ extern "C" int einf_paged_attention_mixed_tiled(const void* q, const void* k_cac
   a.part_acc = part_acc; a.part_ml = part_ml; a.num_tokens = num_tokens; a.status = status;
   const int blocks = num_items * a.blocks_per_tile;
   const int value_lanes = (vdim + 31) / 32;
+#if HEADS_PAD <= 16
+  if (!single && mma_takes(dtype, heads, kv_heads, dim, vdim)) {
+    if (value_lanes <= 1) return launch_mma<1>(a, blocks, stream);
+    if (value_lanes <= 2) return launch_mma<2>(a, blocks, stream);
+    if (value_lanes <= 3) return launch_mma<3>(a, blocks, stream);
+    return launch_mma<4>(a, blocks, stream);
+  }
+#endif
 #define EINF_TILED(QI, VD) EINF_DISPATCH_2(dtype, T, { return launch_tiled<T, QI, VD>(a, blocks, stream); })
   if (single) {
     if (value_lanes <= 1) EINF_TILED(1, 1)

@@ -1400,12 +1400,14 @@ def mixed_tiled_variant(heads: int) -> str:
     return "HEADS_PAD=" + str(next(n for n in (4, 8, 16, 32) if n >= heads))
 
 
-def mixed_tiled_rows(heads: int, kv_heads: int, key_size: int, value_size: int, single: bool) -> int:
-    """Queries a CTA of the tiled score-mixing kernel takes for these sizes (0: it does not take them)."""
+def mixed_tiled_rows(heads: int, kv_heads: int, key_size: int, value_size: int, single: bool,
+                     dtype: torch.dtype = torch.float32) -> int:
+    """Queries a CTA of the tiled score-mixing kernels takes for these sizes (0: they do not take them); 16
+    for the bfloat16 prompt portions that the tensor-core kernel takes."""
     if heads > MIXED_MAX_HEADS:
         return 0
-    fn = _fn("einf_paged_attention_mixed_tiled_rows", [c_int, c_int, c_int, c_int, c_int], mixed_tiled_variant(heads))
-    return int(fn(heads, kv_heads, key_size, value_size, int(single)))
+    fn = _fn("einf_paged_attention_mixed_tiled_rows", [c_int, c_int, c_int, c_int, c_int, c_int], mixed_tiled_variant(heads))
+    return int(fn(heads, kv_heads, key_size, value_size, int(single), BFLOAT16 if dtype == torch.bfloat16 else FLOAT32))
 
 
 def mixed_tiled_splits(blocks: int, rows: int, window: Optional[int], max_context: int) -> int:
@@ -1429,9 +1431,9 @@ def _mixed_tiled(q, k_cache, v_cache, block_table, seq_of_token, positions, out,
         raise ValueError("q_tiles must be int32 [tiles, 4]")
     launches = []
     if num_singles:
-        launches.append((single_tokens, num_singles, 1, mixed_tiled_rows(heads, kv_heads, key_size, value_size, True)))
+        launches.append((single_tokens, num_singles, 1, mixed_tiled_rows(heads, kv_heads, key_size, value_size, True, q.dtype)))
     if num_tiles:
-        launches.append((q_tiles, num_tiles, 0, mixed_tiled_rows(heads, kv_heads, key_size, value_size, False)))
+        launches.append((q_tiles, num_tiles, 0, mixed_tiled_rows(heads, kv_heads, key_size, value_size, False, q.dtype)))
     if not launches or any(rows == 0 for _, _, _, rows in launches):
         return False
     variant = mixed_tiled_variant(heads)

@@ -98,7 +98,8 @@ def test_tiled_score_mixing_decode_splits_its_keys(dev, batch, context, window):
     torch.testing.assert_close(out.cpu(), want, **tol(torch.bfloat16))
 
 
-def test_tiled_score_mixing_far_key_and_window_edge(dev):
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_tiled_score_mixing_far_key_and_window_edge(dev, dtype):
     """One key far back carries the weight: a query whose window still holds it returns its value, the next
     query, for which it has just left the window, does not; in a prompt portion and for a single token."""
     from einf_b200 import ops
@@ -106,7 +107,7 @@ def test_tiled_score_mixing_far_key_and_window_edge(dev):
     heads, kv_heads, size, page_size, window = 4, 2, 32, 16, 100
     needle = 37
     for requests in ([(0, 300)], [(needle + window - 1, 1), (needle + window, 1)], [(100, 60)]):
-        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, torch.float32, heads, kv_heads, size, page_size,
+        (q, k, v, table, seq, pos), scale, _ = _attention_case(dev, dtype, heads, kv_heads, size, page_size,
                                                                requests, window)
         q[:] = 0.0
         q[:, :, 0] = 1.0
@@ -126,7 +127,7 @@ def test_tiled_score_mixing_far_key_and_window_edge(dev):
             p = int(pos[t])
             inside = needle <= p < needle + window
             got = out[t].abs().max().item()
-            assert (abs(got - 7.0) < 1e-3) if inside else got < 6.0, (requests, p, got)
+            assert (abs(got - 7.0) < 1e-3) if inside else got < 6.0, (dtype, requests, p, got)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
