@@ -518,6 +518,7 @@ __global__ void __launch_bounds__(kTiledThreads, 1) paged_attention_mixed_mma_ke
         if (h < heads) {
           const __nv_bfloat16* krow = ks + ((h / per) * kKeyTile + n0 + gl) * ldq + tl * 2;
           const __nv_bfloat16* qrow = qs + (h * kMmaRows + mrow) * ldq + mcol;
+#pragma unroll 4
           for (int d = 0; d < dim; d += 16) {
             uint32_t x[4];
             ldmatrix4(x, qrow + d);
@@ -559,27 +560,51 @@ __global__ void __launch_bounds__(kTiledThreads, 1) paged_attention_mixed_mma_ke
       }
     }
     __syncthreads();
-    // ---- running maximum and sum, a warp per (head, query) row; each weight stays as two bfloat16 terms
-    for (int r = warp; r < heads * kMmaRows; r += kTiledWarps) {
-      float* row = sc + (size_t)r * kScoreStride;
-      const float2 v = *(const float2*)(row + 2 * lane);
-      const float best = warp_max(fmaxf(v.x, v.y));
-      const float before = top[r];
-      const float now = fmaxf(before, best);
-      const float w0 = v.x == -INFINITY ? 0.f : expf(v.x - now);
-      const float w1 = v.y == -INFINITY ? 0.f : expf(v.y - now);
-      const float sum = warp_sum(w0 + w1);
-      const __nv_bfloat16 h0 = __float2bfloat16_rn(w0), h1 = __float2bfloat16_rn(w1);
-      const __nv_bfloat16 l0 = __float2bfloat16_rn(w0 - __bfloat162float(h0)), l1 = __float2bfloat16_rn(w1 - __bfloat162float(h1));
+    // ---- running maximum and sum, a warp per (head, query) row, four rows at a time so that their
+    // reductions overlap; each weight stays in its row's place as two bfloat16 terms
+    for (int r0 = warp; r0 < heads * kMmaRows; r0 += 4 * kTiledWarps) {
+      float2 v[4];
+      float best[4], sum[4], now[4], before[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = r0 + u * kTiledWarps;
+        v[u] = r < heads * kMmaRows ? *(const float2*)(sc + (size_t)r * kScoreStride + 2 * lane) : make_float2(-INFINITY, -INFINITY);
+        best[u] = fmaxf(v[u].x, v[u].y);
+      }
+#pragma unroll
+      for (int step = 16; step > 0; step >>= 1)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) best[u] = fmaxf(best[u], __shfl_xor_sync(0xffffffffu, best[u], step));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = r0 + u * kTiledWarps;
+        before[u] = r < heads * kMmaRows ? top[r] : -INFINITY;
+        now[u] = fmaxf(before[u], best[u]);
+        v[u].x = v[u].x == -INFINITY ? 0.f : expf(v[u].x - now[u]);
+        v[u].y = v[u].y == -INFINITY ? 0.f : expf(v[u].y - now[u]);
+        sum[u] = v[u].x + v[u].y;
+      }
+#pragma unroll
+      for (int step = 16; step > 0; step >>= 1)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sum[u] += __shfl_xor_sync(0xffffffffu, sum[u], step);
       __syncwarp();
-      __nv_bfloat162* terms = (__nv_bfloat162*)row;
-      terms[lane] = __halves2bfloat162(h0, h1);
-      terms[32 + lane] = __halves2bfloat162(l0, l1);
-      if (lane == 0) {
-        const float f = before == -INFINITY ? 0.f : expf(before - now);
-        factor[r] = f;
-        total[r] = fmaf(total[r], f, sum);
-        top[r] = now;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = r0 + u * kTiledWarps;
+        if (r >= heads * kMmaRows) continue;
+        const __nv_bfloat16 h0 = __float2bfloat16_rn(v[u].x), h1 = __float2bfloat16_rn(v[u].y);
+        const __nv_bfloat16 l0 = __float2bfloat16_rn(v[u].x - __bfloat162float(h0));
+        const __nv_bfloat16 l1 = __float2bfloat16_rn(v[u].y - __bfloat162float(h1));
+        __nv_bfloat162* terms = (__nv_bfloat162*)(sc + (size_t)r * kScoreStride);
+        terms[lane] = __halves2bfloat162(h0, h1);
+        terms[32 + lane] = __halves2bfloat162(l0, l1);
+        if (lane == 0) {
+          const float f = before[u] == -INFINITY ? 0.f : expf(before[u] - now[u]);
+          factor[r] = f;
+          total[r] = fmaf(total[r], f, sum[u]);
+          top[r] = now[u];
+        }
       }
     }
     __syncthreads();
