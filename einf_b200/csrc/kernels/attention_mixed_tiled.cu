@@ -686,22 +686,42 @@ __global__ void __launch_bounds__(kTiledThreads) mixed_join_kernel(const __grid_
   const BlockPlace place = block_place<QI>(a);
   if (place.rows <= 0) return;
   const int outs = a.heads * a.vdim;
-  for (int idx = threadIdx.x; idx < place.rows * outs; idx += kTiledThreads) {
-    const int i = idx / outs, o = idx - i * outs;
-    const int h = o / a.vdim;
-    const size_t t = (size_t)place.first_token + i;
-    float best = a.sink ? a.sink[h] : -INFINITY;
-    for (int s = 0; s < a.splits; ++s) best = fmaxf(best, a.part_ml[(((size_t)s * a.num_tokens + t) * a.heads + h) * 2]);
-    float sum = a.sink ? expf(a.sink[h] - best) : 0.f;
-    float value = 0.f;
-    for (int s = 0; s < a.splits; ++s) {
-      const float* ml = a.part_ml + (((size_t)s * a.num_tokens + t) * a.heads + h) * 2;
-      const float w = ml[0] == -INFINITY ? 0.f : expf(ml[0] - best);
-      sum = fmaf(ml[1], w, sum);
-      value = fmaf(a.part_acc[((size_t)s * a.num_tokens + t) * outs + o], w, value);
-    }
-    ((T*)a.out)[t * outs + o] = from_float<T>(value / sum * a.out_scale);
+  constexpr int kBatch = 8;                           // loads in flight before they are used
+  const int idx = blockIdx.y * kTiledThreads + threadIdx.x;
+  if (idx >= place.rows * outs) return;
+  const int i = idx / outs, o = idx - i * outs;
+  const int h = o / a.vdim;
+  const size_t t = (size_t)place.first_token + i;
+  const size_t ml_step = (size_t)a.num_tokens * a.heads * 2, acc_step = (size_t)a.num_tokens * outs;
+  const float* ml = a.part_ml + (t * a.heads + h) * 2;
+  const float* part = a.part_acc + t * outs + o;
+  float best = a.sink ? a.sink[h] : -INFINITY;
+  for (int s0 = 0; s0 < a.splits; s0 += kBatch) {
+    float m[kBatch];
+#pragma unroll
+    for (int e = 0; e < kBatch; ++e) m[e] = s0 + e < a.splits ? ml[(s0 + e) * ml_step] : -INFINITY;
+#pragma unroll
+    for (int e = 0; e < kBatch; ++e) best = fmaxf(best, m[e]);
   }
+  float sum = a.sink ? expf(a.sink[h] - best) : 0.f;
+  float value = 0.f;
+  for (int s0 = 0; s0 < a.splits; s0 += kBatch) {
+    float m[kBatch], l[kBatch], v[kBatch];
+#pragma unroll
+    for (int e = 0; e < kBatch; ++e) {
+      const bool in = s0 + e < a.splits;
+      m[e] = in ? ml[(s0 + e) * ml_step] : -INFINITY;
+      l[e] = in ? ml[(s0 + e) * ml_step + 1] : 0.f;
+      v[e] = in ? part[(s0 + e) * acc_step] : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < kBatch; ++e) {
+      const float w = m[e] == -INFINITY ? 0.f : expf(m[e] - best);
+      sum = fmaf(l[e], w, sum);
+      value = fmaf(v[e], w, value);
+    }
+  }
+  ((T*)a.out)[t * outs + o] = from_float<T>(value / sum * a.out_scale);
 }
 
 }  // namespace einf
@@ -758,7 +778,8 @@ static int launch_mma(const MixedTiledArgs& a, int blocks, cudaStream_t stream) 
   }
   cudaError_t e = launch_pdl(kernel, dim3(blocks, a.splits), kTiledThreads, bytes, stream, a);
   if (e != cudaSuccess || a.splits == 1) return (int)e;
-  return (int)launch_pdl(mixed_join_kernel<__nv_bfloat16, 4>, blocks, kTiledThreads, 0, stream, a);
+  return (int)launch_pdl(mixed_join_kernel<__nv_bfloat16, 4>, dim3(blocks, (a.rows * a.heads * a.vdim + kTiledThreads - 1) / kTiledThreads),
+                         kTiledThreads, 0, stream, a);
 }
 #endif
 
@@ -772,7 +793,8 @@ static int launch_tiled(const MixedTiledArgs& a, int blocks, cudaStream_t stream
   }
   cudaError_t e = launch_pdl(kernel, dim3(blocks, a.splits), kTiledThreads, bytes, stream, a);
   if (e != cudaSuccess || a.splits == 1) return (int)e;
-  return (int)launch_pdl(mixed_join_kernel<T, QI>, blocks, kTiledThreads, 0, stream, a);
+  return (int)launch_pdl(mixed_join_kernel<T, QI>, dim3(blocks, (a.rows * a.heads * a.vdim + kTiledThreads - 1) / kTiledThreads),
+                         kTiledThreads, 0, stream, a);
 }
 
 // Rows per CTA for the given sizes (0: this kernel does not take them; 1 with `single`).

@@ -328,6 +328,7 @@ stream_tail_tokens_kernel(float* __restrict__ residual, const __grid_constant__ 
       for (int r = 0; r < 2; ++r)
 #pragma unroll
         for (int i = 0; i < TB; ++i) dot[r][i] = 0.f;
+#pragma unroll 4
       for (int p = lane; p < pieces; p += 32) {
         float w[2][8];
         load_piece<TW>(gate, (size_t)d0 * hidden + 8 * p, w[0]);
@@ -370,7 +371,7 @@ stream_tail_tokens_kernel(float* __restrict__ residual, const __grid_constant__ 
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
       if (p < pieces) {
-#pragma unroll 4
+#pragma unroll 8
         for (int d = part; d < side; d += 4) {
           float w[8];
           load_piece<TW>(proj_t, (size_t)d * hidden + 8 * p, w);
@@ -425,7 +426,16 @@ stream_tail_tokens_kernel(float* __restrict__ residual, const __grid_constant__ 
       const float v = x[idx];
       history[(size_t)(depth_index + 1) * history_stride + at] = v;
       float acc = 0.f;
-      for (int j = 0; j <= depth_index; ++j) acc = fmaf(depth_weight[j], history[(size_t)j * history_stride + at], acc);
+      constexpr int kBatch = 8;                         // earlier layers' results: several loads in flight
+      for (int j0 = 0; j0 <= depth_index; j0 += kBatch) {
+        float earlier[kBatch];
+#pragma unroll
+        for (int e = 0; e < kBatch; ++e)
+          earlier[e] = j0 + e <= depth_index ? history[(size_t)(j0 + e) * history_stride + at] : 0.f;
+#pragma unroll
+        for (int e = 0; e < kBatch; ++e)
+          if (j0 + e <= depth_index) acc = fmaf(depth_weight[j0 + e], earlier[e], acc);
+      }
       residual[at] = fmaf(newest, v, acc);
     }
   } else {

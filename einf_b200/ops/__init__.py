@@ -1391,7 +1391,7 @@ def stream_tail(
 MIXED_MAX_HEADS = 32
 
 
-MIXED_TILED_TARGET_CTAS = 2 * 148     # the keys of a launch with fewer CTAs than this are split
+NUM_SMS = 148
 _mixed_join_scratch: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
@@ -1410,15 +1410,15 @@ def mixed_tiled_rows(heads: int, kv_heads: int, key_size: int, value_size: int, 
     return int(fn(heads, kv_heads, key_size, value_size, int(single), BFLOAT16 if dtype == torch.bfloat16 else FLOAT32))
 
 
-def mixed_tiled_splits(blocks: int, rows: int, window: Optional[int], max_context: int) -> int:
-    """CTAs that share the keys of one block of ``rows`` queries: enough to fill the device when the
-    launch has few blocks, and no more than the 64-key tiles a query can see."""
+def mixed_tiled_splits(blocks: int, rows: int, window: Optional[int], max_context: int, per_sm: int = 2) -> int:
+    """CTAs that share the keys of one block of ``rows`` queries: as many as still run at once
+    (``per_sm`` CTAs an SM) when the launch has few blocks, and no more than the 64-key tiles a query can see."""
     if not max_context and not window:
         return 1
     keys = max_context or (1 << 30)
     if window:
         keys = min(keys, int(window) + rows - 1)
-    return max(1, min(-(-keys // 64), -(-MIXED_TILED_TARGET_CTAS // max(1, blocks)), 64))
+    return max(1, min(-(-keys // 64), (NUM_SMS * per_sm) // max(1, blocks), 64))
 
 
 def _mixed_tiled(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, slopes, talk, sink,
@@ -1446,7 +1446,9 @@ def _mixed_tiled(q, k_cache, v_cache, block_table, seq_of_token, positions, out,
     )
     global launch_count
     for items, count, single, rows in launches:
-        splits = mixed_tiled_splits(count * (1 if single else -(-128 // rows)), rows, window, max_context)
+        on_tensor_cores = not single and rows == 16 and q.dtype == torch.bfloat16      # one CTA an SM
+        splits = mixed_tiled_splits(count * (1 if single else -(-128 // rows)), rows, window, max_context,
+                                    1 if on_tensor_cores else 2)
         part_acc = part_ml = None
         if splits > 1:
             key = (str(q.device), splits, tokens, heads, value_size)
