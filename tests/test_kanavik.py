@@ -441,7 +441,7 @@ def test_replay_modes(name, dtype, folders):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("size,page,needles", [(24, 16, (0, 25, 60)), (136, 16, (1, 153, 300)), (16, 4, (0, 17, 35))])
+@pytest.mark.parametrize("size,page,needles", [(24, 16, (0, 25, 60)), (120, 16, (1, 137, 280)), (16, 4, (0, 17, 35))])
 def test_a_key_at_the_windows_edge_decides_the_row(dtype, size, page, needles, tmp_path):
     needle_check(tmp_path, dtype, "cuda:0", size, page, needles, needles[-1] + size + 5)
 
