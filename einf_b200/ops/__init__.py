@@ -1451,13 +1451,14 @@ def _mixed_tiled(q, k_cache, v_cache, block_table, seq_of_token, positions, out,
                                     1 if on_tensor_cores else 2)
         part_acc = part_ml = None
         if splits > 1:
-            key = (str(q.device), splits, tokens, heads, value_size)
+            # Buffers by power-of-two size and never given back: a captured graph keeps the address it saw.
+            need = splits * tokens * heads * value_size
+            bucket = max(1 << 16, 1 << (need - 1).bit_length())
+            key = (str(q.device), bucket)
             scratch = _mixed_join_scratch.get(key)
             if scratch is None:
-                scratch = (torch.empty((splits, tokens, heads * value_size), dtype=torch.float32, device=q.device),
-                           torch.empty((splits, tokens, heads, 2), dtype=torch.float32, device=q.device))
-                if len(_mixed_join_scratch) > 16:
-                    _mixed_join_scratch.clear()
+                scratch = (torch.empty(bucket, dtype=torch.float32, device=q.device),
+                           torch.empty(2 * bucket, dtype=torch.float32, device=q.device))
                 _mixed_join_scratch[key] = scratch
             part_acc, part_ml = scratch
         _check(
