@@ -499,9 +499,10 @@ extern "C" int einf_stream_tail(float* residual, const void* pend_a, int a_dtype
   if (hidden <= 0 || side < 0) return (int)cudaErrorInvalidValue;
   const Pending pending{pend_a, a_dtype, a_splits, a_stride, pend_b, b_dtype, b_splits, b_stride};
   if (hidden % 8 == 0 && side > 0 && ((uintptr_t)gate | (uintptr_t)proj_t) % 16 == 0) {
-    // several tokens a CTA: eight for a long step where they fit beside a second CTA, else four
+    // tokens a CTA: eight for a long step where they fit beside a second CTA, else four; one while every token
+    // still gets an SM of its own (the step is then bound by one CTA's instructions, not by the matrices' bytes)
     auto bytes = [&](int each) { return (size_t)(2 * each * hidden + each * side + each * (kTailThreads / 32)) * sizeof(float); };
-    const int each = (num_tokens >= 1024 && bytes(8) <= 100 * 1024) ? 8 : 4;
+    const int each = (num_tokens >= 1024 && bytes(8) <= 100 * 1024) ? 8 : (num_tokens <= 148 ? 1 : 4);
     if (bytes(each) <= 200 * 1024) {
       const int blocks = (num_tokens + each - 1) / each;
 #define EINF_TAIL(TB)                                                                                                   \
@@ -516,6 +517,7 @@ extern "C" int einf_stream_tail(float* residual, const void* pend_a, int a_dtype
                            depth_index, depth_weight, history_stride, hidden, num_tokens);                              \
   })
       if (each == 8) EINF_TAIL(8)
+      if (each == 1) EINF_TAIL(1)
       EINF_TAIL(4)
 #undef EINF_TAIL
     }
