@@ -45,6 +45,7 @@ struct MixedTiledArgs {
   float out_scale;
   int rows, blocks_per_tile, splits;
   int groups_at_once;        // key/value heads whose tiles are in shared memory together
+  int values_shared;         // tensor-core kernel: the values' tile takes the keys' place after the first product
   float* part_acc;           // [splits, tokens, heads * vdim]
   float* part_ml;            // [splits, tokens, heads, 2]
   int num_tokens;
@@ -428,8 +429,8 @@ __device__ __forceinline__ void load_tile_bf16(__nv_bfloat16* __restrict__ tile,
   }
 }
 
-template <int VB>
-__global__ void __launch_bounds__(kTiledThreads, 1) paged_attention_mixed_mma_kernel(const __grid_constant__ MixedTiledArgs a) {
+template <int VB, int MINB>
+__global__ void __launch_bounds__(kTiledThreads, MINB) paged_attention_mixed_mma_kernel(const __grid_constant__ MixedTiledArgs a) {
   constexpr int NT = (kHP * VB + kTiledWarps - 1) / kTiledWarps;      // (head, 32 value columns) tasks a warp may hold
   extern __shared__ float4 smem4[];
   const int heads = a.heads, dim = a.dim, vdim = a.vdim, kv_heads = a.kv_heads;
@@ -437,14 +438,15 @@ __global__ void __launch_bounds__(kTiledThreads, 1) paged_attention_mixed_mma_ke
   const int ldq = dim + 8, ldv = vdim + 8;
   __nv_bfloat16* qs = (__nv_bfloat16*)smem4;                          // [heads * 16, ldq]
   __nv_bfloat16* ks = qs + heads * kMmaRows * ldq;                    // [kv_heads * 64, ldq]
-  __nv_bfloat16* vs = ks + kv_heads * kKeyTile * ldq;                 // [kv_heads * 64, ldv]
-  float* sc = (float*)(vs + kv_heads * kKeyTile * ldv);               // [heads * 16, kScoreStride]
+  const bool shared_kv = a.values_shared != 0;
+  __nv_bfloat16* vs = shared_kv ? ks : ks + kv_heads * kKeyTile * ldq;      // [kv_heads * 64, ldv]
+  float* sc = (float*)(ks + kv_heads * kKeyTile * (shared_kv ? max(ldq, ldv) : ldq + ldv));   // [heads * 16, kScoreStride]
   float* talk_s = sc + heads * kMmaRows * kScoreStride;               // [heads, kHP]
   float* slope_s = talk_s + heads * kHP;                              // [kHP]
   float* top = slope_s + kHP;                                         // [heads * 16]
   float* total = top + heads * kMmaRows;
   float* factor = total + heads * kMmaRows;
-  int* pages = (int*)(factor + heads * kMmaRows);                     // [2, 64]
+  int* pages = (int*)(factor + heads * kMmaRows);                     // [64]
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -493,19 +495,16 @@ __global__ void __launch_bounds__(kTiledThreads, 1) paged_attention_mixed_mma_ke
 
   if (tid < kKeyTile && tile_first < tile_last) {
     const int j = lo + tile_first * kKeyTile + tid;
-    pages[(tile_first & 1) * kKeyTile + tid] = j <= hi ? table[j / a.page_size] : 0;
+    pages[tid] = j <= hi ? table[j / a.page_size] : 0;
   }
   for (int tile = tile_first; tile < tile_last; ++tile) {
     const int j0 = lo + tile * kKeyTile;
     const int count = min(kKeyTile, hi - j0 + 1);
-    const int* tile_pages = pages + (tile & 1) * kKeyTile;
-    if (tid < kKeyTile && tile + 1 < tile_last) {
-      const int j = j0 + kKeyTile + tid;
-      pages[((tile + 1) & 1) * kKeyTile + tid] = j <= hi ? table[j / a.page_size] : 0;
-    }
+    const int* tile_pages = pages;
     __syncthreads();                                  // the tile before is used up; qs and pages are written
     load_tile_bf16(ks, ldq, (const __nv_bfloat16*)a.k_cache, dim, kv_heads, a.page_size, a.num_pages, tile_pages, j0, count, a.status);
-    load_tile_bf16(vs, ldv, (const __nv_bfloat16*)a.v_cache, vdim, kv_heads, a.page_size, a.num_pages, tile_pages, j0, count, a.status);
+    if (!shared_kv)
+      load_tile_bf16(vs, ldv, (const __nv_bfloat16*)a.v_cache, vdim, kv_heads, a.page_size, a.num_pages, tile_pages, j0, count, a.status);
     __syncthreads();
     {
       // ---- raw scores of keys 8 warp .. 8 warp + 7 for every head, then distance, mixing and mask in registers
@@ -560,6 +559,8 @@ __global__ void __launch_bounds__(kTiledThreads, 1) paged_attention_mixed_mma_ke
       }
     }
     __syncthreads();
+    if (shared_kv)                                    // the keys are used up: their place takes the values
+      load_tile_bf16(vs, ldv, (const __nv_bfloat16*)a.v_cache, vdim, kv_heads, a.page_size, a.num_pages, tile_pages, j0, count, a.status);
     // ---- running maximum and sum, a warp per (head, query) row, four rows at a time so that their
     // reductions overlap; each weight stays in its row's place as two bfloat16 terms
     for (int r0 = warp; r0 < heads * kMmaRows; r0 += 4 * kTiledWarps) {
@@ -608,6 +609,10 @@ __global__ void __launch_bounds__(kTiledThreads, 1) paged_attention_mixed_mma_ke
       }
     }
     __syncthreads();
+    if (tid < kKeyTile && tile + 1 < tile_last) {     // this tile's loads are done; the next tile's come after a barrier
+      const int j = j0 + kKeyTile + tid;
+      pages[tid] = j <= hi ? table[j / a.page_size] : 0;
+    }
     // ---- weighted values
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
@@ -756,22 +761,38 @@ static TiledShape tiled_shape(int heads, int kv_heads, int dim, int vdim, int si
   return {0, 0};
 }
 
-static size_t mma_bytes(int heads, int kv_heads, int dim, int vdim) {
-  return (size_t)(heads * 16 * (dim + 8) + kv_heads * kKeyTile * (dim + 8) + kv_heads * kKeyTile * (vdim + 8)) * 2 +
-         (size_t)(heads * 16 * (kKeyTile + 4) + heads * kHP + kHP + 3 * heads * 16 + 2 * kKeyTile) * sizeof(float);
+static size_t mma_bytes(int heads, int kv_heads, int dim, int vdim, bool values_shared) {
+  const int both = values_shared ? (dim > vdim ? dim + 8 : vdim + 8) : dim + 8 + vdim + 8;
+  return (size_t)(heads * 16 * (dim + 8) + kv_heads * kKeyTile * both) * 2 +
+         (size_t)(heads * 16 * (kKeyTile + 4) + heads * kHP + kHP + 3 * heads * 16 + kKeyTile) * sizeof(float);
+}
+
+// How the tensor-core kernel runs for these sizes: two CTAs an SM where the shared memory of two fits (with
+// the values in a place of their own if that fits too, else in the keys' place), else one.  ctas 0: it does not fit.
+struct MmaMode {
+  int ctas, values_shared;
+};
+static MmaMode mma_mode(int heads, int kv_heads, int dim, int vdim) {
+  const size_t half = (size_t)(228 - 2) * 1024 / 2, whole = (size_t)220 * 1024;
+  if (mma_bytes(heads, kv_heads, dim, vdim, false) <= half) return {2, 0};
+  if (mma_bytes(heads, kv_heads, dim, vdim, true) <= half) return {2, 1};
+  if (mma_bytes(heads, kv_heads, dim, vdim, false) <= whole) return {1, 0};
+  if (mma_bytes(heads, kv_heads, dim, vdim, true) <= whole) return {1, 1};
+  return {0, 0};
 }
 
 // The tensor-core kernel takes bfloat16 prompt portions of up to 16 heads whose sizes fit its fragments.
 static bool mma_takes(int dtype, int heads, int kv_heads, int dim, int vdim) {
   return kHP <= 16 && dtype == kBFloat16 && dim % 16 == 0 && vdim % 8 == 0 && vdim <= 128 &&
-         mma_bytes(heads, kv_heads, dim, vdim) <= (size_t)220 * 1024;
+         mma_mode(heads, kv_heads, dim, vdim).ctas > 0;
 }
 
 #if HEADS_PAD <= 16
-template <int VB>
-static int launch_mma(const MixedTiledArgs& a, int blocks, cudaStream_t stream) {
-  auto kernel = paged_attention_mixed_mma_kernel<VB>;
-  const size_t bytes = mma_bytes(a.heads, a.kv_heads, a.dim, a.vdim);
+template <int VB, int MINB>
+static int launch_mma_as(MixedTiledArgs a, int blocks, int values_shared, cudaStream_t stream) {
+  auto kernel = paged_attention_mixed_mma_kernel<VB, MINB>;
+  a.values_shared = values_shared;
+  const size_t bytes = mma_bytes(a.heads, a.kv_heads, a.dim, a.vdim, values_shared != 0);
   if (bytes > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return (int)e;
@@ -780,6 +801,13 @@ static int launch_mma(const MixedTiledArgs& a, int blocks, cudaStream_t stream) 
   if (e != cudaSuccess || a.splits == 1) return (int)e;
   return (int)launch_pdl(mixed_join_kernel<__nv_bfloat16, 4>, dim3(blocks, (a.rows * a.heads * a.vdim + kTiledThreads - 1) / kTiledThreads),
                          kTiledThreads, 0, stream, a);
+}
+
+template <int VB>
+static int launch_mma(const MixedTiledArgs& a, int blocks, cudaStream_t stream) {
+  const MmaMode mode = mma_mode(a.heads, a.kv_heads, a.dim, a.vdim);
+  if (mode.ctas == 2) return launch_mma_as<VB, 2>(a, blocks, mode.values_shared, stream);
+  return launch_mma_as<VB, 1>(a, blocks, mode.values_shared, stream);
 }
 #endif
 
@@ -805,6 +833,12 @@ extern "C" int einf_paged_attention_mixed_tiled_rows(int heads, int kv_heads, in
   return tiled_shape(heads, kv_heads, dim, vdim, single).rows;
 }
 
+// CTAs of the tensor-core kernel that share an SM for these sizes (0: it does not take them).
+extern "C" int einf_paged_attention_mixed_mma_ctas(int heads, int kv_heads, int dim, int vdim, int dtype) {
+  if (heads <= 0 || heads > kHP || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0) return 0;
+  return mma_takes(dtype, heads, kv_heads, dim, vdim) ? mma_mode(heads, kv_heads, dim, vdim).ctas : 0;
+}
+
 // `items`: q_tiles [num_items, 4] with single == 0; token indices [num_items] (or null: tokens 0 .. num_items - 1)
 // with single != 0.  `splits` > 1 needs part_acc [splits, num_tokens, heads * vdim] and part_ml [splits, num_tokens, heads, 2].
 extern "C" int einf_paged_attention_mixed_tiled(const void* q, const void* k_cache, const void* v_cache, int dtype,
@@ -827,6 +861,7 @@ extern "C" int einf_paged_attention_mixed_tiled(const void* q, const void* k_cac
   a.out = out; a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.page_size = page_size;
   a.num_pages = num_pages; a.scale = scale; a.window = window; a.slopes = slopes; a.talk = talk; a.sink = sink;
   a.groups_at_once = tiled_shape(heads, kv_heads, dim, vdim, single).groups;
+  a.values_shared = 0;
   a.out_scale = out_scale; a.rows = rows; a.blocks_per_tile = single ? 1 : (128 + rows - 1) / rows; a.splits = splits;
   a.part_acc = part_acc; a.part_ml = part_ml; a.num_tokens = num_tokens; a.status = status;
   const int blocks = num_items * a.blocks_per_tile;

@@ -1446,9 +1446,11 @@ def _mixed_tiled(q, k_cache, v_cache, block_table, seq_of_token, positions, out,
     )
     global launch_count
     for items, count, single, rows in launches:
-        on_tensor_cores = not single and rows == 16 and q.dtype == torch.bfloat16      # one CTA an SM
-        splits = mixed_tiled_splits(count * (1 if single else -(-128 // rows)), rows, window, max_context,
-                                    1 if on_tensor_cores else 2)
+        per_sm = 2
+        if not single and q.dtype == torch.bfloat16:      # the tensor-core kernel runs one or two CTAs an SM
+            ctas = _fn("einf_paged_attention_mixed_mma_ctas", [c_int, c_int, c_int, c_int, c_int], variant)
+            per_sm = int(ctas(heads, kv_heads, key_size, value_size, BFLOAT16)) or 2
+        splits = mixed_tiled_splits(count * (1 if single else -(-128 // rows)), rows, window, max_context, per_sm)
         part_acc = part_ml = None
         if splits > 1:
             # Buffers by power-of-two size and never given back: a captured graph keeps the address it saw.

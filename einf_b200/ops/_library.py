@@ -50,6 +50,7 @@ LAUNCHERS = {
     "einf_paged_attention_mixed": "attention_mixed",
     "einf_paged_attention_mixed_tiled": "attention_mixed_tiled",
     "einf_paged_attention_mixed_tiled_rows": "attention_mixed_tiled",
+    "einf_paged_attention_mixed_mma_ctas": "attention_mixed_tiled",
     "einf_gated_scan": "recurrence",
     "einf_argmax": "sampling",
     "einf_sample": "sampling",
