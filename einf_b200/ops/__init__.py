@@ -1392,6 +1392,7 @@ MIXED_MAX_HEADS = 32
 
 
 NUM_SMS = 148
+MIXED_KEYS_PER_SPLIT = 64       # a CTA that shares a block's keys takes at least one 64-key tile
 _mixed_join_scratch: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
@@ -1418,7 +1419,7 @@ def mixed_tiled_splits(blocks: int, rows: int, window: Optional[int], max_contex
     keys = max_context or (1 << 30)
     if window:
         keys = min(keys, int(window) + rows - 1)
-    return max(1, min(-(-keys // 64), (NUM_SMS * per_sm) // max(1, blocks), 64))
+    return max(1, min(-(-keys // MIXED_KEYS_PER_SPLIT), (NUM_SMS * per_sm) // max(1, blocks), 64))
 
 
 def _mixed_tiled(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, slopes, talk, sink,
