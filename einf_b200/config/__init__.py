@@ -4,6 +4,7 @@ from .bomipel import BomipelConfig
 from .engine import EngineConfig
 from .kanavik import KanavikConfig
 from .qwen2 import Qwen2Config
+from .rekodra import RekodraConfig
 from .registry import (
     config_class_for,
     config_from_dict,
@@ -18,6 +19,7 @@ register_architecture(Qwen2Config)
 register_architecture(TepavikConfig)
 register_architecture(BomipelConfig)
 register_architecture(KanavikConfig)
+register_architecture(RekodraConfig)
 
 __all__ = [
     "BomipelConfig",
@@ -29,6 +31,7 @@ __all__ = [
     "ModelSpec",
     "PartSpec",
     "Qwen2Config",
+    "RekodraConfig",
     "ScheduleEntry",
     "TensorSpec",
     "TepavikConfig",

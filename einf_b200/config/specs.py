@@ -64,10 +64,13 @@ class ScheduleEntry:
     ``layer`` indexes :attr:`ModelSpec.layers`; naming it twice runs the same
     weights twice.  Each entry owns a cache of its own unless ``cache_from``
     names an earlier entry: then it reads that entry's cache and writes none.
+    ``add_embedding``: the embedding output (the stream as it was before the first entry) is added
+    to the stream once more right before this entry runs, as the repeats of a looped span want it.
     """
 
     layer: int
     cache_from: int | None = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

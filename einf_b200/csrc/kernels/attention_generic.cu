@@ -17,7 +17,9 @@
 // own chunk, counted from position 0 of the sequence.  With a soft cap z the scaled score s becomes
 // z * tanh(s / z) before the softmax.  Keys and values may have different sizes per head.
 // With `keep_first` n > 0 a windowed token also sees the first n positions of its sequence
-// (j < n), at their true positions.  `value_stride` is the distance between two value rows in
+// (j < n), at their true positions.  With `sink` (one float per query head) the softmax's
+// denominator of head h also holds exp(sink[h]): a column with no key and no value, unscaled.
+// `value_stride` is the distance between two value rows in
 // elements: value_size for a cache of its own, the key size when the values are the leading
 // elements of the key rows (a latent cache that holds one row per token for both).
 // The kernel exists twice: for sizes up to 256 and for sizes up to 640 (more registers a lane).
@@ -54,7 +56,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                T* __restrict__ out, int num_rows, int num_heads, int num_kv_heads,
                                int head_size, int value_size, int value_stride, int page_size, int num_pages,
                                int table_width, float scale, int window, int keep_first, int chunk, float softcap,
-                               int* status) {
+                               const float* __restrict__ sink, int* status) {
   __shared__ float q_smem[kWarpsPerBlock][kHeadLimit];
   pdl_launch_dependents();
   pdl_wait();
@@ -140,7 +142,14 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   }
   }
   if (__any_sync(0xffffffffu, bad_page) && lane == 0) atomicOr(status, kStatusBadPage);
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+  float inv = l > 0.f ? 1.f / l : 0.f;
+  if (sink) {
+    // one more term of the denominator, against the larger of the two maxima
+    const float s = sink[h];
+    const float top = fmaxf(m, s);
+    const float keys = (m == -INFINITY) ? 0.f : l * expf(m - top);
+    inv = (m == -INFINITY) ? 0.f : expf(m - top) / (keys + expf(s - top));
+  }
   T* o_row = out + (size_t)row * value_size;
 #pragma unroll
   for (int i = 0; i < kDimsPerLane; ++i) {
@@ -350,7 +359,7 @@ extern "C" int einf_paged_attention_generic(const void* q, const void* k_cache, 
                                             int num_heads, int num_kv_heads, int head_size, int value_size,
                                             int value_stride, int page_size, int num_pages, int table_width,
                                             float scale, int window, int keep_first, int chunk, float softcap,
-                                            int* status, cudaStream_t stream) {
+                                            const float* sink, int* status, cudaStream_t stream) {
   const int rows = num_tokens * num_heads;
   if (rows == 0) return 0;
   if (head_size > kMaxHeadSize || value_size > kMaxHeadSize || head_size <= 0 || value_size <= 0)
@@ -362,12 +371,12 @@ extern "C" int einf_paged_attention_generic(const void* q, const void* k_cache, 
       paged_attention_generic_kernel<T, 256><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
           (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, seq_of_token, positions, (T*)out,
           rows, num_heads, num_kv_heads, head_size, value_size, value_stride, page_size, num_pages, table_width,
-          scale, window, keep_first, chunk, softcap, status);
+          scale, window, keep_first, chunk, softcap, sink, status);
     } else {
       paged_attention_generic_kernel<T, kMaxHeadSize><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
           (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, seq_of_token, positions, (T*)out,
           rows, num_heads, num_kv_heads, head_size, value_size, value_stride, page_size, num_pages, table_width,
-          scale, window, keep_first, chunk, softcap, status);
+          scale, window, keep_first, chunk, softcap, sink, status);
     }
   })
   return (int)cudaGetLastError();

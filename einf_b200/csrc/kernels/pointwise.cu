@@ -14,13 +14,14 @@ namespace einf {
 // Embedding: residual[t, :] = table[token[t], :]   (reference: nn.Embedding,
 // src/einf/executors/torch/qwen.py:744).  With a table of learned position vectors
 // (pos_table [max_positions, hidden]) the row of the token's position is added, unscaled, in
-// 32-bit; a position outside the table sets the same status bit as a bad token.
+// 32-bit; a position outside the table sets the same status bit as a bad token.  The token's row
+// is multiplied by `scale` (1 for most models), in 32-bit.
 // ---------------------------------------------------------------------------
 template <typename TTable>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TTable* __restrict__ table,
                              float* __restrict__ residual, int hidden, int vocab, int* status,
                              const int* __restrict__ positions, const TTable* __restrict__ pos_table,
-                             int max_positions) {
+                             int max_positions, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -35,9 +36,9 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TTable* __res
   const TTable* row = table + (size_t)token * hidden;
   if (pos_table) {
     const TTable* pos = pos_table + (size_t)position * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]) + to_float(pos[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]) * scale + to_float(pos[i]);
   } else {
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]) * scale;
   }
 }
 
@@ -880,6 +881,12 @@ __global__ void act_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up,
 // Value mixing across layers (`value_mix`): 1 = this layer is the source, its values are also
 // left in `shared_values` [T, G * value_size] (32-bit); 2 = its values become
 // (1 - m) v + m shared_values[t] with the scalar m = *mix, before they are cached.
+// Norm weights: with `normalise` 1 and q_weight / k_weight [key_size], a normalised query or key
+// head is multiplied by the weight (one for all query heads, one for all key heads) before the
+// rotation.  With `normalise` 2 the root mean square is taken over all query heads of the row at
+// once (and over all key heads at once) and the weights are [H * key_size] and [G * key_size].
+// With `values_from_keys` the row holds no values, [H query heads | G key heads]: a token's
+// cached value head is its key head as projected (bias added), before norm and rotation.
 // ---------------------------------------------------------------------------
 template <typename TIn, typename T>
 __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, size_t split_stride,
@@ -890,7 +897,8 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
                                       const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                       int rotary_pairs, int interleaved, int value_mix,
                                       float* __restrict__ shared_values, const void* __restrict__ mix, int mix_dtype,
-                                      int* status) {
+                                      const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                                      int values_from_keys, int* status) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -901,14 +909,18 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
   int value_head = -1;
   const int t = (int)(warp / per_token);
   const int item = (int)(warp - (long long)t * per_token);
-  const int width = (num_heads + num_kv_heads) * key_size + num_kv_heads * value_size;
+  const int width = (num_heads + num_kv_heads) * key_size + (values_from_keys ? 0 : num_kv_heads * value_size);
   int size, base;
   T* dst;
   bool unit = normalise != 0;
+  const float* weight = nullptr;     // the norm's weight for this head, indexed by the dimension
+  int section = 0, section_size = 0;  // normalise 2: the part of the row whose root mean square counts
   if (item < num_heads) {
     size = key_size;
     base = item * key_size;
     dst = q_out + ((size_t)t * num_heads + item) * key_size;
+    if (q_weight) weight = normalise == 2 ? q_weight + base : q_weight;
+    section_size = num_heads * key_size;
   } else {
     const int slot = slots ? slots[t] : -1;
     if (slot < 0) return;
@@ -922,10 +934,14 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
       size = key_size;
       base = item * key_size;
       dst = k_cache + (((size_t)page * num_kv_heads + head) * page_size + offset) * key_size;
+      if (k_weight) weight = normalise == 2 ? k_weight + head * key_size : k_weight;
+      section = num_heads * key_size;
+      section_size = num_kv_heads * key_size;
     } else {
       const int head = item - num_heads - num_kv_heads;
       size = value_size;
-      base = (num_heads + num_kv_heads) * key_size + head * value_size;
+      base = values_from_keys ? (num_heads + head) * key_size
+                              : (num_heads + num_kv_heads) * key_size + head * value_size;
       dst = v_cache + (((size_t)page * num_kv_heads + head) * page_size + offset) * value_size;
       unit = false;
       rotate = false;
@@ -947,7 +963,27 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
     }
   }
   float factor = 1.f;
-  if (unit) factor = rsqrtf(warp_sum(ss) / (float)size + eps);
+  if (unit && normalise == 2) {
+    // every warp of the section adds up the same squares in the same order
+    const TIn* whole = qkv + (size_t)t * width + section;
+    float all = 0.f;
+    for (int d = lane; d < section_size; d += 32) {
+      float x = sum_splits(whole + d, splits, split_stride);
+      if (bias) x += bias[section + d];
+      all += x * x;
+    }
+    factor = rsqrtf(warp_sum(all) / (float)section_size + eps);
+  } else if (unit) {
+    factor = rsqrtf(warp_sum(ss) / (float)size + eps);
+  }
+  if (weight) {
+    // the weight comes before the rotation: scale the head now, and its partners as they are fetched
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < size) v[i] *= factor * weight[d];
+    }
+  }
   if (rotate) {
     const float pos = (float)positions[t];
 #pragma unroll
@@ -964,6 +1000,7 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
         }
         float w = sum_splits(row + other, splits, split_stride);
         if (bias) w += bias[base + other];
+        if (weight) w *= factor * weight[other];
         float sn, cs;
         sincosf(pos * inv_freq[pair], &sn, &cs);
         v[i] = leads ? v[i] * cs - w * sn : v[i] * cs + w * sn;
@@ -982,6 +1019,7 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
       }
     }
   }
+  if (weight) factor = 1.f;     // applied above
 #pragma unroll
   for (int i = 0; i < kPerLane; ++i) {
     const int d = lane + 32 * i;
@@ -998,13 +1036,55 @@ __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ b
   }
 }
 
-// out = cap * tanh(out / cap), in place: the soft cap on logits.
-__global__ void softcap_kernel(float* __restrict__ values, long long n, float cap) {
+// Several branches' outputs joined after a norm each: out = scale * sum_i w_i * x_i / rms(x_i), row
+// by row in 32-bit, the root mean square over the row with eps inside the root.  A term may be the
+// partial sums of a split-K product.  One CTA per row; the row's terms are summed twice from
+// global memory (the second read comes from the cache) rather than kept, so any width goes.
+struct JoinTerm {
+  const void* x; int dtype; int splits; long long stride; const float* weight;
+};
+struct JoinArgs {
+  JoinTerm term[4];
+  int terms;
+};
+
+__device__ __forceinline__ float join_value(const JoinTerm& term, size_t at) {
+  if (term.dtype == kFloat32) return sum_splits((const float*)term.x + at, term.splits, (size_t)term.stride);
+  return to_float(((const __nv_bfloat16*)term.x)[at]);
+}
+
+__global__ void norm_join_kernel(const __grid_constant__ JoinArgs a, float eps, float scale, float* __restrict__ out,
+                                 int width) {
+  __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
-  const float inv = 1.f / cap;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-    values[i] = cap * tanhf(values[i] * inv);
+  const size_t row = (size_t)blockIdx.x * width;
+  float factor[4];
+  for (int i = 0; i < a.terms; ++i) {
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+      const float x = join_value(a.term[i], row + d);
+      ss += x * x;
+    }
+    factor[i] = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+  }
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    float v = 0.f;
+    for (int i = 0; i < a.terms; ++i) v += a.term[i].weight[d] * (join_value(a.term[i], row + d) * factor[i]);
+    out[row + d] = scale * v;
+  }
+}
+
+// out = cap * tanh(scale * out / cap), in place: a constant factor and the soft cap on logits;
+// cap 0: the factor alone.
+__global__ void softcap_kernel(float* __restrict__ values, long long n, float cap, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const float inv = cap > 0.f ? 1.f / cap : 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float v = values[i] * scale;
+    values[i] = cap > 0.f ? cap * tanhf(v * inv) : v;
+  }
 }
 
 }  // namespace einf
@@ -1019,12 +1099,12 @@ static inline int pick_threads(int work) {
 
 extern "C" int einf_embed(const int* tokens, const void* table, int table_dtype, float* residual,
                           int num_tokens, int hidden, int vocab, int* status, const int* positions,
-                          const void* pos_table, int max_positions, cudaStream_t stream) {
+                          const void* pos_table, int max_positions, float scale, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   const int threads = pick_threads(hidden);
   EINF_DISPATCH_2(table_dtype, T, {
     return (int)launch_pdl(embed_kernel<T>, num_tokens, threads, 0, stream, tokens, (const T*)table, residual, hidden,
-                           vocab, status, positions, (const T*)pos_table, max_positions);
+                           vocab, status, positions, (const T*)pos_table, max_positions, scale);
   })
 }
 
@@ -1307,9 +1387,12 @@ extern "C" int einf_qkv_norm_store(const void* qkv, int in_dtype, int splits, lo
                                    int num_tokens, int num_heads, int num_kv_heads, int key_size, int value_size,
                                    int normalise, float eps, int page_size, int num_pages, const int* positions,
                                    const float* inv_freq, int rotary_pairs, int interleaved, int value_mix,
-                                   float* shared_values, const void* mix, int mix_dtype, int* status,
+                                   float* shared_values, const void* mix, int mix_dtype, const float* q_weight,
+                                   const float* k_weight, int values_from_keys, int* status,
                                    cudaStream_t stream) {
   if (num_tokens == 0) return 0;
+  if (normalise < 0 || normalise > 2 || ((q_weight || k_weight) && !normalise)) return (int)cudaErrorInvalidValue;
+  if (values_from_keys && (value_size != key_size || value_mix)) return (int)cudaErrorInvalidValue;
   if (rotary_pairs < 0 || 2 * rotary_pairs > key_size || (rotary_pairs > 0 && (!positions || !inv_freq)))
     return (int)cudaErrorInvalidValue;
   if (value_mix && (!shared_values || (value_mix == 2 && !mix))) return (int)cudaErrorInvalidValue;
@@ -1325,7 +1408,7 @@ extern "C" int einf_qkv_norm_store(const void* qkv, int in_dtype, int splits, lo
                              (size_t)split_stride, bias, slots, (T*)q_out, (T*)k_cache, (T*)v_cache, num_tokens,
                              num_heads, num_kv_heads, key_size, value_size, normalise, eps, page_size, num_pages,
                              positions, inv_freq, rotary_pairs, interleaved, value_mix, shared_values, mix, mix_dtype,
-                             status);
+                             q_weight, k_weight, values_from_keys, status);
     })
   })
 }
@@ -1343,10 +1426,30 @@ extern "C" int einf_add_bias(void* out, int dtype, const float* bias, long long 
   return (int)cudaGetLastError();
 }
 
-extern "C" int einf_softcap(float* values, long long n, float cap, cudaStream_t stream) {
+extern "C" int einf_softcap(float* values, long long n, float cap, float scale, cudaStream_t stream) {
   if (n == 0) return 0;
-  if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
+  if (!(cap >= 0.f)) return (int)cudaErrorInvalidValue;
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  return (int)launch_pdl(softcap_kernel, (int)blocks, 256, 0, stream, values, n, cap);
+  return (int)launch_pdl(softcap_kernel, (int)blocks, 256, 0, stream, values, n, cap, scale);
+}
+
+extern "C" int einf_norm_join(int terms,
+                              const void* x0, int d0, int s0, long long st0, const float* w0,
+                              const void* x1, int d1, int s1, long long st1, const float* w1,
+                              const void* x2, int d2, int s2, long long st2, const float* w2,
+                              const void* x3, int d3, int s3, long long st3, const float* w3,
+                              float eps, float scale, float* out, int rows, int width, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (terms < 1 || terms > 4 || width <= 0) return (int)cudaErrorInvalidValue;
+  JoinArgs a;
+  a.terms = terms;
+  a.term[0] = {x0, d0, s0, st0, w0};
+  a.term[1] = {x1, d1, s1, st1, w1};
+  a.term[2] = {x2, d2, s2, st2, w2};
+  a.term[3] = {x3, d3, s3, st3, w3};
+  for (int i = 0; i < terms; ++i)
+    if (!a.term[i].x || !a.term[i].weight || (a.term[i].dtype != kFloat32 && a.term[i].splits > 1))
+      return (int)cudaErrorInvalidValue;
+  return (int)launch_pdl(norm_join_kernel, rows, pick_threads(width), 0, stream, a, eps, scale, out, width);
 }

@@ -525,6 +525,123 @@ __global__ void gated_norm_kernel(const float* __restrict__ y, const T* __restri
 }
 
 // ---------------------------------------------------------------------------
+// The gates of a matrix memory with exponential gating.  Per request and head, token after token:
+//   i = cap tanh((z_i + b_i) / cap),  f = logsigmoid(cap tanh((z_f + b_f) / cap)),
+//   m <- max(f + m, i),   decay = exp(f + m_before - m),   scale = exp(i - m),   floor = exp(-m)
+// where z are the raw gates [T, 2 heads] (input gates, then forget gates; possibly split-K partial
+// sums), m the running maximum that lives in top_state[slot * top_stride + head] (zero after a
+// fresh start; a request without a slot starts from zero and stores nothing).  decay and scale are
+// what the linear recurrence multiplies its state and its input by; they never exceed one.
+// One CTA per request in four phases: the capped logarithms of all its tokens side by side (left
+// in `scale` and `decay`), the maxima by one thread per head (two dependent operations a token, left
+// in `floor`), the three exponentials of all tokens side by side, and the values widened for the
+// recurrence: v_wide[t, h] = [v[t, h] | 1 | 0 ...] of `columns` elements, so that the memory's
+// normaliser (the same recurrence on the keys alone) is one more column of its state.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+memory_gates_kernel(const float* __restrict__ gates, int splits, size_t split_stride, const float* __restrict__ bias,
+                    float cap, const T* __restrict__ v, long long v_stride, float* __restrict__ top_state,
+                    long long top_stride, int num_slots, const int* __restrict__ q_start,
+                    const int* __restrict__ state_slots, float* __restrict__ decay, float* __restrict__ scale,
+                    float* __restrict__ floor, T* __restrict__ v_wide, int heads, int vdim, int columns) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int first = q_start[r], last = q_start[r + 1];
+  const int count = last - first;
+  if (count <= 0) return;
+  const int slot = state_slots[r];
+  const bool kept = slot >= 0 && slot < num_slots;
+  const float inv_cap = 1.f / cap;
+  const int width = 2 * heads;
+  for (int i = threadIdx.x; i < count * heads; i += blockDim.x) {
+    const int t = first + i / heads, h = i % heads;
+    float zi = bias[h], zf = bias[heads + h];
+    for (int s = 0; s < splits; ++s) {
+      zi += gates[(size_t)s * split_stride + (size_t)t * width + h];
+      zf += gates[(size_t)s * split_stride + (size_t)t * width + heads + h];
+    }
+    scale[(size_t)t * heads + h] = cap * tanhf(zi * inv_cap);
+    decay[(size_t)t * heads + h] = log_sigmoid_f(cap * tanhf(zf * inv_cap));
+  }
+  __syncthreads();
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+    float m = kept ? top_state[(long long)slot * top_stride + h] : 0.f;
+    for (int t = first; t < last; ++t) {
+      m = fmaxf(decay[(size_t)t * heads + h] + m, scale[(size_t)t * heads + h]);
+      floor[(size_t)t * heads + h] = m;
+    }
+  }
+  __syncthreads();
+  // the maximum before a token: the one of the token ahead of it, or the slot's (still unchanged)
+  for (int i = threadIdx.x; i < count * heads; i += blockDim.x) {
+    const int t = first + i / heads, h = i % heads;
+    const size_t at = (size_t)t * heads + h;
+    const float before = t > first ? floor[at - heads] : (kept ? top_state[(long long)slot * top_stride + h] : 0.f);
+    const float m = floor[at], log_keep = decay[at], log_in = scale[at];
+    decay[at] = expf(log_keep + before - m);
+    scale[at] = expf(log_in - m);
+  }
+  __syncthreads();
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+    const float m = floor[(size_t)(last - 1) * heads + h];
+    if (kept) top_state[(long long)slot * top_stride + h] = m;
+  }
+  for (int i = threadIdx.x; i < count * heads; i += blockDim.x) {
+    const size_t at = (size_t)(first + i / heads) * heads + i % heads;
+    floor[at] = expf(-floor[at]);
+  }
+  const int wide = heads * columns;
+  for (long long i = threadIdx.x; i < (long long)count * wide; i += blockDim.x) {
+    const int t = first + (int)(i / wide), c = (int)(i % wide);
+    const int h = c / columns, d = c - h * columns;
+    T value = from_float<T>(d == vdim ? 1.f : 0.f);
+    if (d < vdim) value = v[(long long)t * v_stride + h * vdim + d];
+    v_wide[(size_t)t * wide + c] = value;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// What a matrix memory hands on.  y [T, heads * columns] floats is the recurrence's output on the
+// widened values: per head `vdim` numerators and, at column vdim, the normaliser's product with the
+// query.  With c the queries' factor (applied here, to numerators and normaliser alike):
+//   o = c y[:vdim] / (max(|c y[vdim]|, floor) + denominator_eps)
+//   out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate)
+// head by head, in 32-bit.  One warp per (token, head).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void memory_output_kernel(const float* __restrict__ y, const float* __restrict__ floor,
+                                     const T* __restrict__ gate, long long gate_stride,
+                                     const float* __restrict__ weight, T* __restrict__ out, long long pairs, int heads,
+                                     int vdim, int columns, float query_scale, float eps, float denominator_eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long pair = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (pair >= pairs) return;
+  const long long t = pair / heads;
+  const int h = (int)(pair - t * heads);
+  const float* row = y + (t * heads + h) * columns;
+  const float below = fmaxf(fabsf(query_scale * row[vdim]), floor[pair]) + denominator_eps;
+  const float factor = query_scale / below;
+  float ss = 0.f;
+  for (int d = lane; d < vdim; d += 32) {
+    const float o = row[d] * factor;
+    ss += o * o;
+  }
+  const float unit = rsqrtf(warp_sum(ss) / (float)vdim + eps);
+  const T* g_row = gate + t * gate_stride + (long long)h * vdim;
+  T* o_row = out + (t * heads + h) * vdim;
+  for (int d = lane; d < vdim; d += 32) {
+    const float g = to_float(g_row[d]);
+    o_row[d] = from_float<T>(row[d] * factor * unit * weight[h * vdim + d] * (1.f / (1.f + expf(-g))));
+  }
+}
+
+// ---------------------------------------------------------------------------
 // A gated linear recurrence with one state value per channel (a real-gated linear recurrent
 // unit).  Per request and channel c of block b = c / part, token after token:
 //   r = sigmoid(gates[t, b, k] + gate_bias[b, k]),   i = sigmoid(gates[t, b, part + k] + gate_bias[b, part + k]),
@@ -797,5 +914,35 @@ extern "C" int einf_gated_scan(const float* gates, const float* gate_bias, const
       if (e != cudaSuccess) return (int)e;
     }
     return (int)launch_pdl(gated_scan_kernel<T, true>, grid, threads, 0, stream, a);
+  })
+}
+
+extern "C" int einf_memory_gates(const float* gates, int splits, long long split_stride, const float* bias, float cap,
+                                 const void* v, int dtype, long long v_stride, float* top_state, long long top_stride,
+                                 int num_slots, const int* q_start, const int* state_slots, int num_requests,
+                                 float* decay, float* scale, float* floor, void* v_wide, int num_tokens, int heads,
+                                 int vdim, int columns, cudaStream_t stream) {
+  if (num_requests == 0 || num_tokens == 0) return 0;
+  if (heads <= 0 || vdim <= 0 || columns <= vdim || !(cap > 0.f)) return (int)cudaErrorInvalidValue;
+  EINF_DISPATCH_2(dtype, T, {
+    return (int)launch_pdl(memory_gates_kernel<T>, num_requests, 128, 0, stream, gates, splits < 1 ? 1 : splits,
+                           (size_t)split_stride, bias, cap, (const T*)v, v_stride, top_state, top_stride, num_slots,
+                           q_start, state_slots, decay, scale, floor, (T*)v_wide, heads, vdim, columns);
+  })
+}
+
+extern "C" int einf_memory_output(const float* y, const float* floor, const void* gate, int dtype, long long gate_stride,
+                                  const float* weight, void* out, int num_tokens, int heads, int vdim, int columns,
+                                  float query_scale, float eps, float denominator_eps, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (heads <= 0 || vdim <= 0 || columns <= vdim) return (int)cudaErrorInvalidValue;
+  const long long pairs = (long long)num_tokens * heads;
+  const int threads = 128;
+  const long long blocks = (pairs * 32 + threads - 1) / threads;
+  if (blocks >= (1ll << 31)) return (int)cudaErrorInvalidValue;
+  EINF_DISPATCH_2(dtype, T, {
+    return (int)launch_pdl(memory_output_kernel<T>, (int)blocks, threads, 0, stream, y, floor, (const T*)gate,
+                           gate_stride, weight, (T*)out, pairs, heads, vdim, columns, query_scale, eps,
+                           denominator_eps);
   })
 }

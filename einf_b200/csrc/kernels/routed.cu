@@ -3,7 +3,10 @@
 //
 //   einf_router_topk   per token: the `top_k` largest router logits (ties to the lower index),
 //                      their weights sigmoid(z) or softmax(z) over all experts, optionally
-//                      divided by their sum; 32-bit throughout
+//                      divided by their sum; 32-bit throughout.  With a correction the choice goes
+//                      by score + correction (the weights stay the scores); with groups only the
+//                      experts of the `keep` groups of neighbours whose best choice score is
+//                      largest can be chosen
 //   einf_moe_dispatch  counts per expert, offsets (experts in order), the place of every
 //                      (token, choice) in the order sorted by expert, and the rows gathered into
 //                      that order (times the router weight where the weight acts on the input);
@@ -14,7 +17,9 @@
 //   einf_moe_combine   out[t] = sum_s addend[s][t] + sum_j (w_tj) y[place(t, j)], in 32-bit and in
 //                      a fixed order: the experts' outputs of a token (or their split-K partial
 //                      sums), and, for a parallel layer, the other branch's output (possibly
-//                      partial sums too), in one pass
+//                      partial sums too), in one pass; a choice beyond the experts hands the
+//                      token's own row through (times its weight), and the addend may carry a
+//                      sigmoid gate of one number per token
 //
 // A row's result depends on that row, its expert and its weight alone: which other tokens share
 // the batch moves nothing.  (The place of a row inside its expert's range is first come, first
@@ -28,18 +33,24 @@ enum RouterScore : int { kScoreSigmoid = 0, kScoreSoftmax = 1 };
 constexpr int kMaxExpertsPerLane = 32;   // experts up to 1024
 
 __global__ void router_topk_kernel(const float* __restrict__ logits, int splits, size_t split_stride, int num_tokens,
-                                   int num_experts, int top_k, int score, int renormalise,
+                                   int row_width, int num_experts, int top_k, int score, int renormalise,
+                                   const float* __restrict__ correction, int group_count, int group_keep,
                                    int* __restrict__ expert_ids, float* __restrict__ weights) {
-  extern __shared__ float z_all[];   // [warps of the CTA][num_experts]: a token's logits, partial sums added up
+  // per warp of the CTA: [num_experts] what the choice goes by | [num_experts] the scores (with a correction) |
+  // [group_count] 1 for a group that may be chosen from
+  extern __shared__ float z_all[];
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (t >= num_tokens) return;
-  float* z = z_all + (threadIdx.x >> 5) * num_experts;
+  const int per_warp = (correction ? 2 : 1) * num_experts + group_count;
+  float* z = z_all + (threadIdx.x >> 5) * per_warp;
+  float* s_all = correction ? z + num_experts : z;
+  float* group_open = z + (correction ? 2 : 1) * num_experts;
   for (int e = lane; e < num_experts; e += 32) {
     float v = 0.f;
-    for (int s = 0; s < splits; ++s) v += logits[(size_t)s * split_stride + (size_t)t * num_experts + e];
+    for (int s = 0; s < splits; ++s) v += logits[(size_t)s * split_stride + (size_t)t * row_width + e];
     z[e] = v;
   }
   __syncwarp();
@@ -52,6 +63,46 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int splits,
     for (int e = lane; e < num_experts; e += 32) sum += expf(z[e] - z_max);
     denominator = warp_sum(sum);
   }
+  if (correction) {
+    // the scores themselves, and what the choice goes by in their place
+    __syncwarp();
+    for (int e = lane; e < num_experts; e += 32) {
+      const float w = score == kScoreSoftmax ? expf(z[e] - z_max) / denominator : 1.f / (1.f + expf(-z[e]));
+      s_all[e] = w;
+      z[e] = w + correction[e];
+    }
+    __syncwarp();
+  }
+  if (group_count > 0) {
+    // a group's score is its best choice score; the `group_keep` best groups stay open (ties to the lower index)
+    const int per_group = num_experts / group_count;
+    for (int g = lane; g < group_count; g += 32) group_open[g] = 0.f;
+    __syncwarp();
+    for (int j = 0; j < group_keep; ++j) {
+      float best = -INFINITY;
+      int best_g = 0x7fffffff;
+      for (int g = lane; g < group_count; g += 32) {
+        if (group_open[g] != 0.f) continue;
+        float top = -INFINITY;
+        for (int i = 0; i < per_group; ++i) top = fmaxf(top, z[g * per_group + i]);
+        if (top > best || best_g == 0x7fffffff) {
+          best = top;
+          best_g = g;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, o);
+        const int other_g = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (other_g != 0x7fffffff && (best_g == 0x7fffffff || other > best || (other == best && other_g < best_g))) {
+          best = other;
+          best_g = other_g;
+        }
+      }
+      if (lane == 0 && best_g != 0x7fffffff) group_open[best_g] = 1.f;
+      __syncwarp();
+    }
+  }
   uint32_t taken = 0;   // bit i: expert lane + 32 i is chosen already
   float chosen_sum = 0.f;
   for (int j = 0; j < top_k; ++j) {
@@ -59,6 +110,7 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int splits,
     int best_e = 0x7fffffff;
     for (int e = lane, i = 0; e < num_experts; e += 32, ++i) {
       if (taken & (1u << i)) continue;
+      if (group_count > 0 && group_open[e / (num_experts / group_count)] == 0.f) continue;
       const float v = z[e];
       if (v > best || (v == best && e < best_e) || best_e == 0x7fffffff) {
         best = v;
@@ -75,7 +127,9 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int splits,
       }
     }
     if ((best_e & 31) == lane) taken |= 1u << (best_e >> 5);
-    const float w = score == kScoreSoftmax ? expf(best - z_max) / denominator : 1.f / (1.f + expf(-best));
+    float w;
+    if (correction) w = s_all[best_e];
+    else w = score == kScoreSoftmax ? expf(best - z_max) / denominator : 1.f / (1.f + expf(-best));
     chosen_sum += w;
     if (lane == 0) {
       expert_ids[(size_t)t * top_k + j] = best_e;
@@ -292,26 +346,45 @@ __device__ __forceinline__ float sum_strided(const T* __restrict__ p, int count,
 // One thread a (token, column), so that a decode step's handful of tokens still spreads over the GPU;
 // with hundreds of tokens a thread takes kColumns columns 128 apart (a quarter of the CTAs, and a
 // token's places and experts are read once for four columns).
-template <typename TY, typename TA, int kColumns>
+template <typename TY, typename TA, typename TX, int kColumns>
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ expert_ids,
                                    const int* __restrict__ place,
                                    const float* __restrict__ weights, int scale_outputs, const TA* __restrict__ addend,
                                    int splits, size_t split_stride, float* __restrict__ out, int num_experts,
-                                   int top_k, int hidden, int y_splits, size_t y_stride) {
+                                   int top_k, int hidden, int y_splits, size_t y_stride,
+                                   const TX* __restrict__ identity_x, int num_identity,
+                                   const float* __restrict__ gate_logits, int gate_width, int gate_column,
+                                   int gate_splits, size_t gate_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.y;
   const int d0 = blockIdx.x * (128 * kColumns) + threadIdx.x;
   float v[kColumns];
+  float addend_gate = 1.f;
+  if (gate_logits) {
+    const float z = sum_strided(gate_logits + (size_t)t * gate_width + gate_column, gate_splits, gate_stride);
+    addend_gate = 1.f / (1.f + expf(-z));
+  }
 #pragma unroll
   for (int c = 0; c < kColumns; ++c) {
     const int d = d0 + 128 * c;
     v[c] = (addend && d < hidden) ? sum_strided(addend + (size_t)t * hidden + d, splits, split_stride) : 0.f;
+    if (gate_logits) v[c] *= addend_gate;
   }
   for (int j = 0; j < top_k; ++j) {
     const int p = t * top_k + j;
     const int e = expert_ids[p];
+    if (e >= num_experts && e < num_experts + num_identity) {
+      // an expert that hands the token through: its weight times the token's own row
+      const float w = weights[p];
+#pragma unroll
+      for (int c = 0; c < kColumns; ++c) {
+        const int d = d0 + 128 * c;
+        if (d < hidden) v[c] += w * to_float(identity_x[(size_t)t * hidden + d]);
+      }
+      continue;
+    }
     if (e < 0 || e >= num_experts) continue;
     const TY* row = y + (size_t)place[p] * hidden;
     const float w = scale_outputs ? weights[p] : 1.f;
@@ -336,16 +409,22 @@ moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ expert_ids,
 using namespace einf;
 
 extern "C" int einf_router_topk(const float* logits, int splits, long long split_stride, int num_tokens,
-                                int num_experts, int top_k, int score, int renormalise, int* expert_ids,
+                                int row_width, int num_experts, int top_k, int score, int renormalise,
+                                const float* correction, int group_count, int group_keep, int* expert_ids,
                                 float* weights, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
-  if (num_experts <= 0 || num_experts > 32 * kMaxExpertsPerLane || top_k <= 0 || top_k > num_experts)
+  if (num_experts <= 0 || num_experts > 32 * kMaxExpertsPerLane || top_k <= 0 || top_k > num_experts ||
+      row_width < num_experts)
+    return (int)cudaErrorInvalidValue;
+  if (group_count < 0 || (group_count > 0 && (num_experts % group_count || group_keep <= 0 || group_keep > group_count ||
+                                              top_k > group_keep * (num_experts / group_count))))
     return (int)cudaErrorInvalidValue;
   const int threads = 128;
   const int blocks = (num_tokens * 32 + threads - 1) / threads;
-  return (int)launch_pdl(router_topk_kernel, blocks, threads, (size_t)(threads / 32) * num_experts * sizeof(float), stream,
-                         logits, splits < 1 ? 1 : splits, (size_t)split_stride, num_tokens, num_experts, top_k, score,
-                         renormalise, expert_ids, weights);
+  const size_t per_warp = (size_t)(correction ? 2 : 1) * num_experts + group_count;
+  return (int)launch_pdl(router_topk_kernel, blocks, threads, (size_t)(threads / 32) * per_warp * sizeof(float), stream,
+                         logits, splits < 1 ? 1 : splits, (size_t)split_stride, num_tokens, row_width, num_experts, top_k,
+                         score, renormalise, correction, group_count, group_keep, expert_ids, weights);
 }
 
 // x: [T, hidden]; expert_ids, weights, place: [T * top_k]; work: [3 E + 1] int32 (offsets are its last
@@ -395,17 +474,25 @@ extern "C" int einf_moe_gemm(const void* x, int x_dtype, const void* w, int w_dt
 extern "C" int einf_moe_combine(const void* y, int y_dtype, const int* expert_ids, const int* place,
                                 const float* weights, int scale_outputs, const void* addend, int addend_dtype,
                                 int splits, long long split_stride, float* out, int num_tokens, int num_experts,
-                                int top_k, int hidden, int y_splits, cudaStream_t stream) {
+                                int top_k, int hidden, int y_splits, const void* identity_x, int identity_dtype,
+                                int num_identity, const float* gate_logits, int gate_width, int gate_column,
+                                int gate_splits, long long gate_stride, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (num_tokens > 65535) return (int)cudaErrorInvalidValue;
+  if (num_identity < 0 || (num_identity > 0 && (!identity_x || !weights))) return (int)cudaErrorInvalidValue;
+  if (gate_logits && (!addend || gate_column < 0 || gate_column >= gate_width)) return (int)cudaErrorInvalidValue;
   const bool many = num_tokens >= 128;
   const dim3 grid(many ? (hidden + 511) / 512 : (hidden + 127) / 128, num_tokens);
   EINF_DISPATCH_2(y_dtype, TY, {
     EINF_DISPATCH_2(addend_dtype, TA, {
-      return (int)launch_pdl(many ? moe_combine_kernel<TY, TA, 4> : moe_combine_kernel<TY, TA, 1>, grid, dim3(128), 0, stream, (const TY*)y, expert_ids, place,
-                             weights, scale_outputs, (const TA*)addend, splits, (size_t)split_stride, out,
-                             num_experts, top_k, hidden, y_splits < 1 ? 1 : y_splits,
-                             (size_t)num_tokens * top_k * hidden);
+      EINF_DISPATCH_2(identity_dtype, TX, {
+        return (int)launch_pdl(many ? moe_combine_kernel<TY, TA, TX, 4> : moe_combine_kernel<TY, TA, TX, 1>, grid,
+                               dim3(128), 0, stream, (const TY*)y, expert_ids, place,
+                               weights, scale_outputs, (const TA*)addend, splits, (size_t)split_stride, out,
+                               num_experts, top_k, hidden, y_splits < 1 ? 1 : y_splits,
+                               (size_t)num_tokens * top_k * hidden, (const TX*)identity_x, num_identity, gate_logits,
+                               gate_width, gate_column, gate_splits < 1 ? 1 : gate_splits, (size_t)gate_stride);
+      })
     })
   })
 }

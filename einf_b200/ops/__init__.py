@@ -115,10 +115,12 @@ def _fn(symbol: str, argtypes, variant: str = ""):
 
 # ---------------------------------------------------------------------------
 def embed(tokens: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, status: torch.Tensor,
-          positions: Optional[torch.Tensor] = None, position_table: Optional[torch.Tensor] = None) -> None:
-    """``residual[t] = table[tokens[t]]`` as float; a token outside the table sets the status word.
+          positions: Optional[torch.Tensor] = None, position_table: Optional[torch.Tensor] = None,
+          scale: float = 1.0) -> None:
+    """``residual[t] = scale * table[tokens[t]]`` as float (the product in 32-bit); a token outside the
+    table sets the status word.
     With ``position_table [max_positions, hidden]`` (the table's dtype) the row ``position_table[positions[t]]``
-    is added in 32-bit; a position beyond it sets the status word too."""
+    is added in 32-bit, unscaled; a position beyond it sets the status word too."""
     vocab, hidden = table.shape
     max_positions, pos_ptr, table_ptr = 0, 0, 0
     if position_table is not None:
@@ -131,10 +133,11 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, sta
     if residual.shape != (tokens.shape[0], hidden):
         raise ValueError(f"residual is {tuple(residual.shape)}, expected {(tokens.shape[0], hidden)}")
     fn = _fn("einf_embed", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                            c_int, c_void_p])
+                            c_int, c_float, c_void_p])
     _check(
         fn(_dev(tokens, "tokens"), _dev(table, "table"), _code(table), _dev(residual, "residual"),
-           tokens.shape[0], hidden, vocab, _dev(status, "status"), pos_ptr, table_ptr, max_positions, _stream()),
+           tokens.shape[0], hidden, vocab, _dev(status, "status"), pos_ptr, table_ptr, max_positions, float(scale),
+           _stream()),
         "embed",
     )
 
@@ -538,6 +541,7 @@ def paged_attention_generic(
     softcap: Optional[float] = None,
     keep_first: int = 0,
     values_in_keys: Optional[int] = None,
+    sink: Optional[torch.Tensor] = None,
 ) -> None:
     """Causal attention of every token of the batch over the pages of its request.
 
@@ -549,8 +553,12 @@ def paged_attention_generic(
     that many positions (blocks counted from position 0); ``softcap`` z: scores become
     ``z * tanh(score / z)`` before the softmax.  ``values_in_keys`` n (with ``v_cache`` None): a
     token's value is the first n elements of its key row (one cached row serves as both).
+    ``sink`` (float32 ``[heads]``): the softmax's denominator of head h also holds ``exp(sink[h])``,
+    unscaled, with no key and no value.
     """
     tokens, num_heads, head_size = q.shape
+    if sink is not None and (sink.dtype != torch.float32 or sink.shape != (num_heads,)):
+        raise ValueError(f"sink must be float32 [{num_heads}]")
     num_pages, num_kv_heads, page_size, size = k_cache.shape
     if values_in_keys is not None:
         if v_cache is not None or not 0 < values_in_keys <= size:
@@ -574,7 +582,7 @@ def paged_attention_generic(
     fn = _fn(
         "einf_paged_attention_generic",
         [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p],
     )
     _check(
         fn(_dev(q, "q"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), _code(q),
@@ -582,7 +590,7 @@ def paged_attention_generic(
            _opt(positions, "positions", torch.int32), _dev(out, "out"), tokens, num_heads, num_kv_heads,
            head_size, value_size, value_stride, page_size, num_pages, block_table.shape[1], float(scale),
            int(window) if window else 0, int(keep_first) if window else 0, int(chunk) if chunk else 0,
-           float(softcap) if softcap else 0.0, _dev(status, "status"), _stream()),
+           float(softcap) if softcap else 0.0, _opt(sink, "sink", torch.float32), _dev(status, "status"), _stream()),
         "paged_attention_generic",
     )
 
@@ -691,6 +699,10 @@ def qkv_norm_store(
     value_mix: Optional[str] = None,
     shared_values: Optional[torch.Tensor] = None,
     mix: Optional[torch.Tensor] = None,
+    q_norm_weight: Optional[torch.Tensor] = None,
+    k_norm_weight: Optional[torch.Tensor] = None,
+    norm_rows: bool = False,
+    values_from_keys: bool = False,
 ) -> None:
     """The general form of bias, position encoding and cache write.  With ``inv_freq`` (float32,
     n entries; needs ``positions``) the first 2n dimensions of every query and key head are rotated
@@ -702,9 +714,26 @@ def qkv_norm_store(
     ``q_out [tokens, heads, key_size]`` and keys and values into the pages at ``slots``.  A row of
     ``qkv`` (or of its float32 split-K partial sums) is ``[heads * key_size | kv_heads * key_size |
     kv_heads * value_size]``; ``num_kv_heads`` 0 means the row holds queries only (the layer reads
-    another layer's pages); ``slots`` None writes no keys or values.  Caches are ``[pages, kv_heads, page, key_size]`` and ``[..., value_size]``."""
+    another layer's pages); ``slots`` None writes no keys or values.  Caches are ``[pages, kv_heads, page, key_size]`` and ``[..., value_size]``.
+    ``q_norm_weight`` / ``k_norm_weight`` (float32; need ``unit_eps``): the normalised queries and keys
+    are multiplied by a weight before any rotation, ``[key_size]`` shared by all heads, or, with
+    ``norm_rows``, ``[heads * key_size]`` and ``[kv_heads * key_size]`` while the root mean square is taken
+    over all heads of the row at once instead of head by head.  ``values_from_keys``: the row holds no
+    values (``[queries | keys]``); a token's cached values are its keys as projected (with bias),
+    before norm and rotation, so ``value_size`` is ``key_size``."""
     tokens = qkv.shape[-2]
-    width = (num_heads + num_kv_heads) * key_size + num_kv_heads * value_size
+    width = (num_heads + num_kv_heads) * key_size + (0 if values_from_keys else num_kv_heads * value_size)
+    if values_from_keys and (value_size != key_size or value_mix is not None):
+        raise ValueError("values taken from the keys have the keys' size and are not mixed across layers")
+    norm_mode = 0 if unit_eps is None else (2 if norm_rows else 1)
+    for name, weight, heads in (("q_norm_weight", q_norm_weight, num_heads), ("k_norm_weight", k_norm_weight, num_kv_heads)):
+        if weight is None:
+            continue
+        if not norm_mode:
+            raise ValueError(f"{name} needs unit_eps")
+        wanted = heads * key_size if norm_rows else key_size
+        if weight.dtype != torch.float32 or weight.shape != (wanted,):
+            raise ValueError(f"{name} must be float32 [{wanted}]")
     splits, stride = _maybe_split(qkv, tokens, width, "qkv")
     if q_out.numel() != tokens * num_heads * key_size:
         raise ValueError("q_out must hold [tokens, heads, key_size]")
@@ -740,17 +769,19 @@ def qkv_norm_store(
         "einf_qkv_norm_store",
         [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-         c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+         c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     )
     _check(
         fn(_dev(qkv, "qkv"), _code(qkv), splits, stride, _code(q_out), _opt(bias, "bias", torch.float32),
            _opt(slots, "slots", torch.int32) if k_ptr else 0, _dev(q_out, "q_out"), k_ptr, v_ptr, tokens,
-           num_heads, num_kv_heads, key_size, value_size, 0 if unit_eps is None else 1,
+           num_heads, num_kv_heads, key_size, value_size, norm_mode,
            float(unit_eps or 0.0), page_size, num_pages,
            _opt(positions, "positions", torch.int32) if pairs else 0,
            _opt(inv_freq, "inv_freq", torch.float32) if pairs else 0, pairs, 1 if interleaved else 0, mix_code,
            _opt(shared_values, "shared_values", torch.float32) if mix_code else 0,
-           _opt(mix, "mix", torch.float32) if mix_code == 2 else 0, FLOAT32, _dev(status, "status"), _stream()),
+           _opt(mix, "mix", torch.float32) if mix_code == 2 else 0, FLOAT32,
+           _opt(q_norm_weight, "q_norm_weight", torch.float32), _opt(k_norm_weight, "k_norm_weight", torch.float32),
+           1 if values_from_keys else 0, _dev(status, "status"), _stream()),
         "qkv_norm_store",
     )
 
@@ -870,24 +901,37 @@ ROUTER_SCORES = {"sigmoid": 0, "softmax": 1}
 
 
 def router_topk(logits: torch.Tensor, top_k: int, score: str, renormalise: bool, expert_ids: torch.Tensor,
-                weights: torch.Tensor) -> None:
-    """Per row of float32 ``logits [tokens, experts]`` (or split-K partial sums ``[splits, tokens, experts]``,
-    added up here): the ``top_k`` experts with the largest logits
+                weights: torch.Tensor, num_experts: Optional[int] = None, correction: Optional[torch.Tensor] = None,
+                groups: Optional[Tuple[int, int]] = None) -> None:
+    """Per row of float32 ``logits [tokens, width]`` (or split-K partial sums ``[splits, tokens, width]``,
+    added up here): the ``top_k`` experts with the largest scores
     (ties to the lower index) into ``expert_ids`` (int32) and their weights into ``weights`` (float32),
     both ``[tokens, top_k]``, best first.  A weight is ``sigmoid(z)`` or the softmax over all experts;
-    ``renormalise`` divides the chosen weights by their sum."""
-    tokens, experts = logits.shape[-2:]
-    splits, stride = _maybe_split(logits, tokens, experts, "logits")
+    ``renormalise`` divides the chosen weights by their sum.  The experts are the first ``num_experts``
+    columns of a row (default: all of them; further columns belong to someone else).  With
+    ``correction`` (float32 ``[num_experts]``) the choice goes by ``score + correction`` while the weights
+    stay the scores.  With ``groups = (count, keep)`` the experts form ``count`` equal groups of
+    neighbours and only those of the ``keep`` groups whose best choice score is largest can be chosen."""
+    tokens, width = logits.shape[-2:]
+    experts = width if num_experts is None else int(num_experts)
+    splits, stride = _maybe_split(logits, tokens, width, "logits")
     if logits.dtype != torch.float32 or weights.dtype != torch.float32 or expert_ids.dtype != torch.int32:
         raise TypeError("router_topk takes float32 logits and weights and int32 expert ids")
     if expert_ids.shape != (tokens, top_k) or weights.shape != (tokens, top_k):
         raise ValueError("expert_ids and weights must be [tokens, top_k]")
-    if not 0 < top_k <= experts or experts > 1024:
-        raise UnsupportedSize(f"top_k {top_k} of {experts} experts (at most 1024)")
-    fn = _fn("einf_router_topk", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                  c_void_p])
+    if not 0 < top_k <= experts <= width or experts > 1024:
+        raise UnsupportedSize(f"top_k {top_k} of {experts} experts (at most 1024) in rows of {width}")
+    if correction is not None and (correction.dtype != torch.float32 or correction.shape != (experts,)):
+        raise ValueError(f"correction must be float32 [{experts}]")
+    count, keep = (0, 0) if groups is None else (int(groups[0]), int(groups[1]))
+    if groups is not None:
+        if count <= 0 or experts % count or not 0 < keep <= count or top_k > keep * (experts // count):
+            raise ValueError(f"{experts} experts in {count} groups of which {keep} are kept cannot give {top_k} choices")
+    fn = _fn("einf_router_topk", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                  c_int, c_void_p, c_void_p, c_void_p])
     _check(
-        fn(_dev(logits, "logits"), splits, stride, tokens, experts, top_k, ROUTER_SCORES[score], 1 if renormalise else 0,
+        fn(_dev(logits, "logits"), splits, stride, tokens, width, experts, top_k, ROUTER_SCORES[score],
+           1 if renormalise else 0, _opt(correction, "correction", torch.float32), count, keep,
            _dev(expert_ids, "expert_ids"), _dev(weights, "weights"), _stream()),
         "router_topk",
     )
@@ -971,10 +1015,16 @@ def moe_gemm(x: torch.Tensor, weight: torch.Tensor, offsets: torch.Tensor, out: 
 
 
 def moe_combine(y: torch.Tensor, expert_ids: torch.Tensor, place: torch.Tensor, weights: torch.Tensor,
-                scale_outputs: bool, addend: Optional[torch.Tensor], out: torch.Tensor, num_experts: int) -> None:
+                scale_outputs: bool, addend: Optional[torch.Tensor], out: torch.Tensor, num_experts: int,
+                identity_input: Optional[torch.Tensor] = None, num_identity: int = 0,
+                addend_gate: Optional[Tuple[torch.Tensor, int]] = None) -> None:
     """``out[t] = addend[t] + sum_j y[place[t, j]]`` (times ``weights[t, j]`` with ``scale_outputs``) as
     float32: the experts' outputs of every token added up in the order of its choices, after the
-    ``addend`` (``[tokens, hidden]`` or float32 partial sums ``[splits, tokens, hidden]``; may be None)."""
+    ``addend`` (``[tokens, hidden]`` or float32 partial sums ``[splits, tokens, hidden]``; may be None).
+    A choice ``num_experts <= e < num_experts + num_identity`` is an expert that hands its input
+    through: it adds ``weights[t, j] * identity_input[t]`` (``[tokens, hidden]``).  ``addend_gate``
+    ``(logits, column)``: the addend is multiplied by ``sigmoid(logits[t, column])``, one number per
+    token, with ``logits`` float32 ``[tokens, width]`` or split-K partial sums of it."""
     tokens, hidden = out.shape
     top_k = expert_ids.shape[1]
     y_splits = y.shape[0] if y.dim() == 3 else 1
@@ -986,25 +1036,42 @@ def moe_combine(y: torch.Tensor, expert_ids: torch.Tensor, place: torch.Tensor, 
         splits, stride = _maybe_split(addend, tokens, hidden, "addend")
         splits = max(splits, 1)
         addend_code, addend_ptr = _code(addend), _dev(addend, "addend")
+    identity_ptr, identity_code = 0, FLOAT32
+    if num_identity:
+        if identity_input is None or identity_input.shape != (tokens, hidden):
+            raise ValueError("experts that hand their input through need identity_input [tokens, hidden]")
+        identity_ptr, identity_code = _dev(identity_input, "identity_input"), _code(identity_input)
+    gate_ptr, gate_width, gate_column, gate_splits, gate_stride = 0, 0, 0, 1, 0
+    if addend_gate is not None:
+        gate, gate_column = addend_gate
+        if addend is None or gate.dtype != torch.float32 or gate.shape[-2] != tokens or \
+                not 0 <= gate_column < gate.shape[-1]:
+            raise ValueError("addend_gate needs an addend and float32 logits [tokens, width] with the column inside")
+        gate_width = gate.shape[-1]
+        gate_splits, gate_stride = _maybe_split(gate, tokens, gate_width, "addend_gate")
+        gate_splits = max(gate_splits, 1)
+        gate_ptr = _dev(gate, "addend_gate")
     fn = _fn(
         "einf_moe_combine",
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_int,
-         c_int, c_int, c_int, c_int, c_void_p],
+         c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p],
     )
     _check(
         fn(_dev(y, "y"), _code(y), _opt(expert_ids, "expert_ids", torch.int32), _opt(place, "place", torch.int32),
            _opt(weights, "weights", torch.float32), 1 if scale_outputs else 0, addend_ptr, addend_code, splits, stride,
-           _dev(out, "out"), tokens, int(num_experts), top_k, hidden, y_splits, _stream()),
+           _dev(out, "out"), tokens, int(num_experts), top_k, hidden, y_splits, identity_ptr, identity_code,
+           int(num_identity), gate_ptr, gate_width, int(gate_column), gate_splits, gate_stride, _stream()),
         "moe_combine",
     )
 
 
-def softcap(values: torch.Tensor, cap: float) -> None:
-    """``values = cap * tanh(values / cap)`` in place (float32)."""
+def softcap(values: torch.Tensor, cap: Optional[float], scale: float = 1.0) -> None:
+    """``values = cap * tanh(scale * values / cap)`` in place (float32); without a cap (None)
+    ``values = scale * values``."""
     if values.dtype != torch.float32:
         raise TypeError("softcap takes float32 values")
-    fn = _fn("einf_softcap", [c_void_p, c_longlong, c_float, c_void_p])
-    _check(fn(_dev(values, "values"), values.numel(), float(cap), _stream()), "softcap")
+    fn = _fn("einf_softcap", [c_void_p, c_longlong, c_float, c_float, c_void_p])
+    _check(fn(_dev(values, "values"), values.numel(), float(cap or 0.0), float(scale), _stream()), "softcap")
 
 
 def _rows_of(x: torch.Tensor, name: str) -> int:
@@ -1246,6 +1313,146 @@ def gated_norm(
            tokens, width, parts, float(eps), 1 if gate_first else 0, kinds[gate_kind], _stream()),
         "gated_norm",
     )
+
+
+def memory_value_columns(vdim: int) -> int:
+    """Columns of a matrix memory's state that carries its normaliser beside its ``vdim`` value columns:
+    one more, filled up to a multiple of four (what the streaming recurrence kernel's 16-byte accesses take)."""
+    return (vdim + 1 + 3) // 4 * 4
+
+
+def memory_gates(
+    gates: torch.Tensor,
+    bias: torch.Tensor,
+    cap: float,
+    v: torch.Tensor,
+    top_state: torch.Tensor,
+    q_start: torch.Tensor,
+    state_slots: torch.Tensor,
+    decay: torch.Tensor,
+    scale: torch.Tensor,
+    floor: torch.Tensor,
+    v_wide: torch.Tensor,
+    heads: int,
+    vdim: int,
+) -> None:
+    """The exponential gates of a matrix memory, stabilised by a running maximum, in 32-bit.
+    ``gates`` float32 ``[tokens, 2 heads]`` (or split-K partial sums of it) holds per head the raw
+    input gate, then the raw forget gate; with ``bias [2 heads]`` and the cap c::
+
+        i_t = c tanh((z_i + b_i) / c)          f_t = logsigmoid(c tanh((z_f + b_f) / c))
+        m_t = max(f_t + m_(t-1), i_t)          decay_t = exp(f_t + m_(t-1) - m_t)
+        scale_t = exp(i_t - m_t)               floor_t = exp(-m_t)
+
+    over each request's tokens in order; ``m`` is read from and written back to ``top_state
+    [slots, heads]`` (float32, slot stride may be larger; a fresh request's row is zero).  ``decay``,
+    ``scale``, ``floor``: float32 ``[tokens, heads]``.  The same launch widens the values for the
+    recurrence: ``v_wide [tokens, heads * columns]`` (v's dtype) is ``v [tokens, heads * vdim]``
+    (columns of a wider matrix are fine) with a column of ones behind every head's values and zeros
+    up to ``columns``."""
+    tokens = v.shape[0]
+    columns = v_wide.shape[1] // max(heads, 1)
+    splits, stride = _maybe_split(gates, tokens, 2 * heads, "gates")
+    if gates.dtype != torch.float32 or bias.dtype != torch.float32 or bias.shape != (2 * heads,):
+        raise ValueError(f"gates must be float32 [tokens, {2 * heads}] and bias float32 [{2 * heads}]")
+    for name, t in (("decay", decay), ("scale", scale), ("floor", floor)):
+        if t.dtype != torch.float32 or t.shape != (tokens, heads) or not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous float32 {(tokens, heads)}")
+    if v.shape != (tokens, heads * vdim) or v_wide.shape != (tokens, heads * columns) or columns <= vdim or \
+            v_wide.dtype != v.dtype or not v_wide.is_contiguous():
+        raise ValueError("v must be [tokens, heads * vdim] and v_wide contiguous [tokens, heads * columns], columns > vdim")
+    if top_state.dtype != torch.float32 or top_state.shape[1] != heads or top_state.stride(1) != 1:
+        raise ValueError(f"top_state must be float32 [slots, {heads}]")
+    requests = state_slots.shape[0]
+    if tokens == 0 or requests == 0:
+        return
+    fn = _fn(
+        "einf_memory_gates",
+        [c_void_p, c_int, c_longlong, c_void_p, c_float, c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_int,
+         c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    )
+    _check(
+        fn(_dev(gates, "gates"), splits, stride, _dev(bias, "bias"), float(cap), v.data_ptr(), _code(v), _rows_of(v, "v"),
+           top_state.data_ptr(), top_state.stride(0), top_state.shape[0], _opt(q_start, "q_start", torch.int32),
+           _opt(state_slots, "state_slots", torch.int32), requests, _dev(decay, "decay"), _dev(scale, "scale"),
+           _dev(floor, "floor"), _dev(v_wide, "v_wide"), tokens, heads, vdim, columns, _stream()),
+        "memory_gates",
+    )
+
+
+def memory_output(
+    y: torch.Tensor,
+    floor: torch.Tensor,
+    gate: torch.Tensor,
+    weight: torch.Tensor,
+    out: torch.Tensor,
+    heads: int,
+    vdim: int,
+    query_scale: float,
+    eps: float,
+    denominator_eps: float,
+) -> None:
+    """What a matrix memory hands on, in 32-bit.  ``y`` float32 ``[tokens, heads * columns]`` is the
+    recurrence's output on the widened values: per head ``vdim`` numerators, then the normaliser's
+    product with the query.  With ``c = query_scale`` (the queries' factor, applied here)::
+
+        o = c y[:vdim] / (max(|c y[vdim]|, floor) + denominator_eps)
+        out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate)
+
+    head by head; ``floor`` float32 ``[tokens, heads]``, ``weight`` float32 ``[heads * vdim]``, ``gate`` and
+    ``out`` ``[tokens, heads * vdim]`` of one dtype (``gate`` may be columns of a wider matrix)."""
+    tokens = y.shape[0]
+    columns = y.shape[1] // max(heads, 1)
+    if y.dtype != torch.float32 or not y.is_contiguous() or y.shape != (tokens, heads * columns) or columns <= vdim:
+        raise ValueError("y must be contiguous float32 [tokens, heads * columns] with columns > vdim")
+    if floor.dtype != torch.float32 or floor.shape != (tokens, heads) or not floor.is_contiguous():
+        raise ValueError(f"floor must be contiguous float32 {(tokens, heads)}")
+    if gate.shape != (tokens, heads * vdim) or out.shape != gate.shape or gate.dtype != out.dtype:
+        raise ValueError("gate and out must be [tokens, heads * vdim] of one dtype")
+    if weight.dtype != torch.float32 or weight.shape != (heads * vdim,):
+        raise ValueError(f"weight must be float32 [{heads * vdim}]")
+    if vdim > MAX_STATE_ROWS * 2:
+        raise UnsupportedSize(f"value heads of up to {MAX_STATE_ROWS * 2} elements, not {vdim}")
+    if tokens == 0:
+        return
+    fn = _fn(
+        "einf_memory_output",
+        [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+         c_float, c_float, c_void_p],
+    )
+    _check(
+        fn(_dev(y, "y"), _dev(floor, "floor"), gate.data_ptr(), _code(gate), _rows_of(gate, "gate"),
+           _dev(weight, "weight"), _dev(out, "out"), tokens, heads, vdim, columns, float(query_scale), float(eps),
+           float(denominator_eps), _stream()),
+        "memory_output",
+    )
+
+
+def norm_join(terms, weights, eps: float, out: torch.Tensor, scale: float = 1.0) -> None:
+    """``out = scale * sum_i weights[i] * terms[i] / sqrt(mean(terms[i]^2) + eps)``, row by row in
+    32-bit: several branches' outputs, each RMS-normed over the row with a weight of its own, added
+    up.  A term is ``[tokens, width]`` (float32 or bfloat16) or float32 split-K partial sums
+    ``[splits, tokens, width]``; ``weights`` float32 ``[width]`` each; ``out`` float32 ``[tokens, width]``.
+    Up to four terms."""
+    tokens, width = out.shape
+    if out.dtype != torch.float32 or not out.is_contiguous():
+        raise TypeError("out must be contiguous float32")
+    if not 0 < len(terms) <= 4 or len(weights) != len(terms):
+        raise UnsupportedSize(f"one to four terms with a weight each, got {len(terms)} and {len(weights)}")
+    packed = []
+    for term, weight in zip(terms, weights):
+        splits, stride = _maybe_split(term, tokens, width, "term")
+        if weight.dtype != torch.float32 or weight.shape != (width,):
+            raise ValueError(f"a weight must be float32 [{width}]")
+        packed.append((_dev(term, "term"), _code(term), max(splits, 1), stride, _dev(weight, "weight")))
+    while len(packed) < 4:
+        packed.append((0, FLOAT32, 0, 0, 0))
+    if tokens == 0:
+        return
+    fn = _fn("einf_norm_join", [c_int] + [c_void_p, c_int, c_int, c_longlong, c_void_p] * 4 +
+             [c_float, c_float, c_void_p, c_int, c_int, c_void_p])
+    flat = [value for term in packed for value in term]
+    _check(fn(len(terms), *flat, float(eps), float(scale), _dev(out, "out"), tokens, width, _stream()), "norm_join")
 
 
 #: head sizes the tensor-core attention kernels take (one build per size)

@@ -52,6 +52,9 @@ LAUNCHERS = {
     "einf_paged_attention_mixed_tiled_rows": "attention_mixed_tiled",
     "einf_paged_attention_mixed_mma_ctas": "attention_mixed_tiled",
     "einf_gated_scan": "recurrence",
+    "einf_memory_gates": "recurrence",
+    "einf_memory_output": "recurrence",
+    "einf_norm_join": "pointwise",
     "einf_argmax": "sampling",
     "einf_sample": "sampling",
     "einf_report": "sampling",

@@ -20,8 +20,15 @@ head) takes ``slope_h (i - j)`` off the score of query i and key j; ``talking_he
 the heads' scores by ``sum_g talk[h, g] score_g`` (a stored matrix over all query heads, whatever
 their key/value head); ``sink`` puts ``exp(sink_h)`` of a stored number per head into the softmax's
 denominator, with no key and no value; ``output_scale`` multiplies the mixed values before they are
-rounded for the output projection.  Such a layer runs a kernel of its own, which computes all
-heads of a query together (``ops.paged_attention_mixed``).
+rounded for the output projection.  A layer with slopes or a mixing matrix runs a kernel of its
+own, which computes all heads of a query together (``ops.paged_attention_mixed``); a sink alone is
+taken by the general kernels.
+
+``qk_norm_weight`` (with ``qk_unit_eps``): the normalised queries and keys are multiplied by stored
+weights before any rotation: ``"head"``, one weight of the head's size for all query heads and one
+for all key heads; ``"row"``, weights over all heads, and the root mean square is taken over the
+whole projection at once instead of head by head.  ``values: "keys"``: the layer has no value
+projection; a token's values are its keys as projected, before norm and rotation.
 """
 from __future__ import annotations
 
@@ -44,7 +51,13 @@ class PagedAttention(Mixer):
         specs = {"q_proj.weight": TensorSpec((heads * size, hidden))}
         if own_kv:
             specs["k_proj.weight"] = TensorSpec((kv_heads * size, hidden))
-            specs["v_proj.weight"] = TensorSpec((kv_heads * value_size, hidden))
+            if spec.get("values", "projected") != "keys":
+                specs["v_proj.weight"] = TensorSpec((kv_heads * value_size, hidden))
+        if spec.get("qk_norm_weight"):
+            rows = spec["qk_norm_weight"] == "row"
+            specs["q_norm.weight"] = TensorSpec((heads * size if rows else size,), "scale")
+            if own_kv:
+                specs["k_norm.weight"] = TensorSpec((kv_heads * size if rows else size,), "scale")
         specs["o_proj.weight"] = TensorSpec((hidden, heads * value_size))
         if spec.get("qkv_bias", False):
             specs["q_proj.bias"] = TensorSpec((heads * size,), "bias")
@@ -64,7 +77,7 @@ class PagedAttention(Mixer):
     @staticmethod
     def _mixes_scores(spec) -> bool:
         """Whether the heads' scores meet before the softmax (a kernel of its own computes them)."""
-        return bool(spec.get("distance_slopes") or spec.get("talking_heads") or spec.get("sink"))
+        return bool(spec.get("distance_slopes") or spec.get("talking_heads"))
 
     @staticmethod
     def _is_general(spec) -> bool:
@@ -76,6 +89,7 @@ class PagedAttention(Mixer):
             or spec.get("keep_first") or spec.get("value_mix")
             or spec["position"].get("layout", "halves") != "halves"
             or PagedAttention._mixes_scores(spec) or spec.get("output_scale") is not None
+            or spec.get("sink") or spec.get("values", "projected") != "projected"
         )
 
     @staticmethod
@@ -83,7 +97,8 @@ class PagedAttention(Mixer):
         """A general layer still runs the tcgen05 attention kernels (which know the chunked mask and
         the soft cap) when its keys and values have one size that those kernels take."""
         size = int(spec["head_size"])
-        return dtype == torch.bfloat16 and (spec.get("value_head_size") or size) == size and size in (64, 128)
+        return dtype == torch.bfloat16 and (spec.get("value_head_size") or size) == size and size in (64, 128) \
+            and not spec.get("sink")
 
     @classmethod
     def kernel_libraries(cls, spec, runtime):
@@ -140,7 +155,28 @@ class PagedAttention(Mixer):
             raise ValueError(f"window must be positive, got {self.window}")
         if self.chunk is not None and self.chunk <= 0:
             raise ValueError(f"chunk must be positive, got {self.chunk}")
-        names = ["q_proj"] if self.shared_kv else ["q_proj", "k_proj", "v_proj"]
+        self.values_from_keys = spec.get("values", "projected") == "keys"
+        if spec.get("values", "projected") not in ("projected", "keys"):
+            raise ValueError(f"values must be projected or keys, got {spec.get('values')!r}")
+        if self.values_from_keys and (self.shared_kv or self.value_size != self.head_size or spec.get("value_mix")
+                                      or spec.get("qkv_bias", False)):
+            raise ValueError("a layer whose values are its keys has keys of its own, of the values' size, unmixed, no bias")
+        self.qk_norm_weight = spec.get("qk_norm_weight")
+        if self.qk_norm_weight not in (None, "head", "row"):
+            raise ValueError(f"qk_norm_weight must be head or row, got {self.qk_norm_weight!r}")
+        if self.qk_norm_weight and self.qk_unit_eps is None:
+            raise ValueError("qk_norm_weight needs qk_unit_eps")
+        self.q_norm_weight = self.k_norm_weight = None
+        if self.qk_norm_weight:
+            self.q_norm_weight = runtime.vector(tensors["q_norm.weight"])
+            if not self.shared_kv:
+                self.k_norm_weight = runtime.vector(tensors["k_norm.weight"])
+        if self.shared_kv:
+            names = ["q_proj"]
+        elif self.values_from_keys:
+            names = ["q_proj", "k_proj"]
+        else:
+            names = ["q_proj", "k_proj", "v_proj"]
         matrices = [tensors[n + ".weight"] for n in names]
         if len({m.dtype for m in matrices}) > 1:
             matrices = [m.to(torch.float32) for m in matrices]
@@ -173,10 +209,14 @@ class PagedAttention(Mixer):
                 self.slopes = torch.tensor(slopes, dtype=torch.float64).to(torch.float32).to(runtime.device)
             if spec.get("talking_heads"):
                 self.talk = runtime.vector(tensors["talk"])
-            if spec.get("sink"):
-                self.sink = runtime.vector(tensors["sink"])
+            if self.qk_norm_weight or self.values_from_keys:
+                raise ValueError("a layer that mixes its heads' scores has no weighted norm and values of its own")
         elif self.output_scale != 1.0:
             raise ValueError("output_scale is applied by the score-mixing kernel only")
+        if spec.get("sink"):
+            if self.softcap or self.chunk or self.keep_first:
+                raise ValueError("a sink comes without a soft cap, chunks or kept positions")
+            self.sink = runtime.vector(tensors["sink"])
         self.fast = not self.general and ops.has_fast_attention(runtime.dtype, self.head_size)
         self.general_fast = self.general and not self.mixes_scores and self._general_on_tensor_cores(spec, runtime.dtype)
 
@@ -206,7 +246,9 @@ class PagedAttention(Mixer):
                 0 if self.shared_kv else self.num_kv_heads, self.head_size, self.value_size, self.qk_unit_eps,
                 ctx.status, positions=ctx.positions, inv_freq=self.position.inv_freq,
                 interleaved=getattr(self.position, "interleaved", False), value_mix=self.value_mix,
-                shared_values=shared_values, mix=self.mix,
+                shared_values=shared_values, mix=self.mix, q_norm_weight=self.q_norm_weight,
+                k_norm_weight=self.k_norm_weight, norm_rows=self.qk_norm_weight == "row",
+                values_from_keys=self.values_from_keys,
             )
         else:
             self.position.encode_and_store(
@@ -272,5 +314,5 @@ class PagedAttention(Mixer):
         ops.paged_attention_generic(
             q, cache.k, cache.v, ctx.block_tables[cache.group], ctx.seq_of_token, ctx.positions,
             out, self.scale, self.window, ctx.status, chunk=self.chunk, softcap=self.softcap,
-            keep_first=self.keep_first,
+            keep_first=self.keep_first, sink=self.sink,
         )

@@ -9,7 +9,9 @@ token (``qwen.py:772-773``); here only the wanted rows reach the head.
 
 With ``max_positions`` in its spec the embedding also has a learned vector per position,
 ``positions [max_positions, hidden]``, added unscaled in the same kernel: ``h0[t] = table[token[t]]
-+ positions[position[t]]``; a position beyond the table sets the step's status word.
++ positions[position[t]]``; a position beyond the table sets the step's status word.  With ``scale``
+the token's row is multiplied by that constant (in 32-bit, as it enters the residual stream).  The
+head's ``scale`` multiplies the logits (before a soft cap, if there is one too).
 """
 from __future__ import annotations
 
@@ -38,13 +40,15 @@ class TokenEmbedding(Part):
         self.table = runtime.matrix(tensors["weight"])
         self.hidden_size = int(spec["hidden_size"])
         self.position_table = runtime.matrix(tensors["positions"]) if spec.get("max_positions") else None
+        self.scale = float(spec.get("scale") or 1.0)
 
     def forward(self, ctx) -> torch.Tensor:
         residual = torch.empty((ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=self.table.device)
         if self.position_table is None:
-            ops.embed(ctx.token_ids, self.table, residual, ctx.status)
+            ops.embed(ctx.token_ids, self.table, residual, ctx.status, scale=self.scale)
         else:
-            ops.embed(ctx.token_ids, self.table, residual, ctx.status, ctx.positions, self.position_table)
+            ops.embed(ctx.token_ids, self.table, residual, ctx.status, ctx.positions, self.position_table,
+                      scale=self.scale)
         return residual
 
 
@@ -59,7 +63,7 @@ class LinearHead(Part):
     @classmethod
     def kernel_libraries(cls, spec, runtime):
         return ("gemm_simt",) + (("gemm_tcgen05",) if runtime.dtype == torch.bfloat16 else ()) + \
-            (("pointwise",) if spec.get("softcap") else ())
+            (("pointwise",) if spec.get("softcap") or spec.get("scale") else ())
 
     def __init__(self, spec, tensors, runtime, tied=None):
         super().__init__(spec, tensors, runtime)
@@ -67,9 +71,10 @@ class LinearHead(Part):
         self.weight = tied if tied is not None else runtime.matrix(tensors["weight"])
         #: ``softcap`` c: logits become ``c * tanh(logits / c)``
         self.softcap = float(spec["softcap"]) if spec.get("softcap") else None
+        self.scale = float(spec["scale"]) if spec.get("scale") is not None else 1.0
 
     def forward(self, x: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
         logits = ops.project(x, self.weight, status, out_dtype=torch.float32, allow_partial=False)
-        if self.softcap is not None:
-            ops.softcap(logits, self.softcap)
+        if self.softcap is not None or self.scale != 1.0:
+            ops.softcap(logits, self.softcap, self.scale)
         return logits

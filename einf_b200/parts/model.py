@@ -133,8 +133,16 @@ class DecoderModel:
         """Run the step's tokens through every schedule entry; float logits ``[S, vocab]``
         at ``ctx.logit_rows``."""
         residual = self.embedding.forward(ctx)
+        # the stream is updated in place: entries that take the embedding output again get a copy of it
+        first = residual.clone() if any(entry.add_embedding for entry in self.schedule) else None
         pending = None
         for index, entry in enumerate(self.schedule):
+            if entry.add_embedding:
+                # one more float32 term of the pending output, which the entry's first norm adds up
+                terms = [first[None]]
+                if pending is not None:
+                    terms.insert(0, (pending if pending.dim() == 3 else pending[None]).to(torch.float32))
+                pending = torch.cat(terms, dim=0) if len(terms) > 1 else terms[0]
             pending = self.blocks[entry.layer].forward(residual, pending, ctx, caches[index])
         if getattr(self.final_norm, "takes_status", False):
             x = self.final_norm.forward(pending, residual, rows=ctx.logit_rows, status=ctx.status)

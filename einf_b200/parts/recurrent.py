@@ -272,3 +272,99 @@ class GatedLinearRecurrence(Mixer):
             ctx.state_slots, out, self.output_scale, max_q_len=ctx.max_q_len,
         )
         return ops.project(out, self.out_weight, ctx.status)
+
+
+@register_part("mixer", "matrix_memory")
+class MatrixMemory(_RecurrentMixer):
+    """A matrix memory with exponential gates (the mLSTM of xLSTM: Beck et al., "xLSTM: Extended Long
+    Short-Term Memory").  Per head a state ``S [dim, vdim]``, a normaliser ``n [dim]`` and the running
+    maximum m of the gates' logarithms, which starts at zero::
+
+        i_t = c tanh((W_i h + b_i) / c)            f_t = logsigmoid(c tanh((W_f h + b_f) / c))
+        m_t = max(f_t + m_(t-1), i_t)
+        S_t = exp(f_t + m_(t-1) - m_t) S_(t-1) + exp(i_t - m_t) k_t v_t^T          (n_t likewise, with k_t alone)
+        o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + denominator_eps)
+
+    with ``q = query_scale W_q h`` and the cap c (``gate_cap``).  Every head's o is divided by its root mean
+    square, the heads together are multiplied by a stored weight and by ``sigmoid(W_g h)`` and
+    projected.  The normaliser rides along as one more value column (a column of ones behind every
+    head's values), so S and n pass through the recurrence kernel of the other mixers as one state
+    ``[dim, columns]``; a kernel before it turns the raw gates into the recurrence's per-token decay and
+    scale, a kernel behind it divides, normalises and gates.  Gates, maximum, state, the division
+    and the norm are 32-bit; the two gate projections leave 32-bit values in both precisions."""
+
+    @classmethod
+    def tensor_specs(cls, spec):
+        hidden, heads, dim, vdim = spec["hidden_size"], spec["num_heads"], spec["head_size"], spec["value_head_size"]
+        return {
+            "q_proj.weight": TensorSpec((heads * dim, hidden)),
+            "k_proj.weight": TensorSpec((heads * dim, hidden)),
+            "v_proj.weight": TensorSpec((heads * vdim, hidden)),
+            "g_proj.weight": TensorSpec((heads * vdim, hidden)),
+            "i_proj.weight": TensorSpec((heads, hidden)),
+            "i_proj.bias": TensorSpec((heads,), "bias"),
+            "f_proj.weight": TensorSpec((heads, hidden)),
+            "f_proj.bias": TensorSpec((heads,), "forget_bias"),
+            "norm.weight": TensorSpec((heads * vdim,), "scale"),
+            "o_proj.weight": TensorSpec((hidden, heads * vdim)),
+        }
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.heads = int(spec["num_heads"])
+        self.dim = int(spec["head_size"])
+        self.vdim = int(spec["value_head_size"])
+        self.eps = float(spec["eps"])
+        self.gate_cap = float(spec["gate_cap"])
+        self.query_scale = float(spec.get("query_scale", self.dim ** -0.5))
+        self.denominator_eps = float(spec["denominator_eps"])
+        if not self.gate_cap > 0:
+            raise ValueError(f"gate_cap must be positive, got {self.gate_cap}")
+        if self.dim > ops.MAX_STATE_ROWS:
+            raise ops.UnsupportedSize(f"head size {self.dim}: the recurrence kernel takes up to {ops.MAX_STATE_ROWS}")
+        self.columns = ops.memory_value_columns(self.vdim)
+        matrices = [tensors[n + "_proj.weight"] for n in ("q", "k", "v", "g")]
+        if len({m.dtype for m in matrices}) > 1:
+            matrices = [m.to(torch.float32) for m in matrices]
+        self.in_weight = runtime.matrix(torch.cat(matrices, dim=0))
+        gates = [tensors["i_proj.weight"], tensors["f_proj.weight"]]
+        if len({m.dtype for m in gates}) > 1:
+            gates = [m.to(torch.float32) for m in gates]
+        self.gate_weight = runtime.matrix(torch.cat(gates, dim=0))                        # [2 heads, hidden]: input gates, forget gates
+        self.gate_bias = runtime.vector(torch.cat([tensors["i_proj.bias"].float(), tensors["f_proj.bias"].float()]))
+        self.out_weight = runtime.matrix(tensors["o_proj.weight"])
+        self.norm_weight = runtime.vector(tensors["norm.weight"])
+        self.state_floats = self.heads * self.dim * self.columns
+        self.state_shape = (self.heads, self.dim, self.columns)
+
+    def cache_need(self):
+        # S with the normaliser as one of its columns, then the running maximum of every head; rows of
+        # whole 16-byte pieces, which the streaming recurrence kernel wants
+        return StateNeed(((self.state_floats + self.heads + 3) // 4 * 4,), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        tokens, device = x.shape[0], x.device
+        heads, keys, values = self.heads, self.heads * self.dim, self.heads * self.vdim
+        proj = ops.project(x, self.in_weight, ctx.status, allow_partial=False)
+        q, k = proj[:, :keys], proj[:, keys:2 * keys]
+        v, gate = proj[:, 2 * keys:2 * keys + values], proj[:, 2 * keys + values:]
+        raw_gates = ops.project(x, self.gate_weight, ctx.status, out_dtype=torch.float32)   # [T, 2 heads], or partial sums
+        state = self._state(cache)
+        slots = state.shape[0]
+        memory = state[:, :self.state_floats].view(slots, heads, self.dim, self.columns)
+        top = state[:, self.state_floats:self.state_floats + heads]
+        decay = torch.empty((tokens, heads), dtype=torch.float32, device=device)
+        scale = torch.empty_like(decay)
+        floor = torch.empty_like(decay)
+        v_wide = torch.empty((tokens, heads * self.columns), dtype=proj.dtype, device=device)
+        ops.memory_gates(raw_gates, self.gate_bias, self.gate_cap, v, top, ctx.q_start, ctx.state_slots, decay, scale,
+                         floor, v_wide, heads, self.vdim)
+        y = torch.empty((tokens, heads * self.columns), dtype=torch.float32, device=device)
+        ops.linear_recurrence(
+            q, k, v_wide, memory, ctx.q_start, ctx.state_slots, y, heads, heads, self.dim, self.columns,
+            token_decay=decay, token_scale=scale, max_q_len=ctx.max_q_len,
+        )
+        out = torch.empty((tokens, values), dtype=self.runtime.dtype, device=device)
+        ops.memory_output(y, floor, gate, self.norm_weight, out, heads, self.vdim, self.query_scale, self.eps,
+                          self.denominator_eps)
+        return ops.project(out, self.out_weight, ctx.status)

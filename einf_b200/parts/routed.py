@@ -6,6 +6,16 @@ weights by their sum); an expert is ``down(silu(gate(u)) * up(u))`` without bias
 ``weight_on: "input"`` the expert sees ``u = w x`` and its output is added as it is; with ``"output"``
 it sees x and its output is multiplied by w.
 
+Optional, each from the spec.  ``correction``: a stored number per router output that is added to the
+scores for the choice alone (the weights stay the scores).  ``groups`` (``count``, ``keep``): the router's
+outputs form equal groups of neighbours, and only those of the ``keep`` groups whose best choice score
+is largest can be chosen.  ``num_identity``: the router has that many outputs beyond the experts;
+one of those, when chosen, hands the token through unchanged (times its weight) and has no tensors.
+They count in the softmax, in the groups and in ``top_k`` like any expert.  ``shared`` (an
+``intermediate_size``): one more gated feed-forward that every token takes, added to the sum; with
+``shared_gate`` its output is multiplied by ``sigmoid(w . x)``, one stored row and one number per token
+(the row rides along in the router's product).
+
 The tokens never go through the host: the (token, choice) pairs are sorted by expert on the device,
 the two products run over the sorted rows expert by expert in one launch each, and one kernel adds
 a token's expert outputs up in 32-bit, together with another branch's output when the layer runs
@@ -28,7 +38,17 @@ class RoutedMLP(FeedForward):
     @classmethod
     def tensor_specs(cls, spec):
         hidden, inter, experts = spec["hidden_size"], spec["intermediate_size"], spec["num_experts"]
-        specs = {"router.weight": TensorSpec((experts, hidden))}
+        outputs = experts + int(spec.get("num_identity") or 0)
+        specs = {"router.weight": TensorSpec((outputs, hidden))}
+        if spec.get("correction"):
+            specs["router.correction"] = TensorSpec((outputs,), "small")
+        if spec.get("shared"):
+            shared = int(spec["shared"])
+            specs["shared.gate_proj.weight"] = TensorSpec((shared, hidden))
+            specs["shared.up_proj.weight"] = TensorSpec((shared, hidden))
+            specs["shared.down_proj.weight"] = TensorSpec((hidden, shared))
+            if spec.get("shared_gate"):
+                specs["shared.gate.weight"] = TensorSpec((1, hidden))
         for e in range(experts):
             specs[f"experts.{e}.gate_proj.weight"] = TensorSpec((inter, hidden))
             specs[f"experts.{e}.up_proj.weight"] = TensorSpec((inter, hidden))
@@ -53,9 +73,34 @@ class RoutedMLP(FeedForward):
         if weight_on not in ("input", "output"):
             raise ValueError(f"weight_on must be input or output, got {weight_on!r}")
         self.weight_on_input = weight_on == "input"
-        if not 0 < self.top_k <= self.num_experts:
-            raise ValueError(f"top_k {self.top_k} of {self.num_experts} experts")
-        self.router_weight = runtime.matrix(tensors["router.weight"])
+        self.num_identity = int(spec.get("num_identity") or 0)
+        self.num_outputs = self.num_experts + self.num_identity
+        if not 0 < self.top_k <= self.num_outputs:
+            raise ValueError(f"top_k {self.top_k} of {self.num_outputs} router outputs")
+        if self.num_identity and self.weight_on_input:
+            raise ValueError("experts that hand their input through take their weight on the output")
+        self.groups = None
+        if spec.get("groups"):
+            self.groups = (int(spec["groups"]["count"]), int(spec["groups"]["keep"]))
+            count, keep = self.groups
+            if count <= 0 or self.num_outputs % count or not 0 < keep <= count or \
+                    self.top_k > keep * (self.num_outputs // count):
+                raise ValueError(f"{self.num_outputs} router outputs in {count} groups of which {keep} are kept "
+                                 f"cannot give {self.top_k} choices")
+        self.correction = runtime.vector(tensors["router.correction"]) if spec.get("correction") else None
+        self.shared_size = int(spec.get("shared") or 0)
+        self.shared_gated = bool(self.shared_size and spec.get("shared_gate"))
+        router_rows = [tensors["router.weight"]]
+        if self.shared_gated:
+            router_rows.append(tensors["shared.gate.weight"])
+        if len({m.dtype for m in router_rows}) > 1:
+            router_rows = [m.to(torch.float32) for m in router_rows]
+        # the shared expert's gate is one more row of the router's product
+        self.router_weight = runtime.matrix(torch.cat(router_rows, dim=0))
+        if self.shared_size:
+            self.shared_gate_up = runtime.matrix(torch.cat(
+                [tensors["shared.gate_proj.weight"], tensors["shared.up_proj.weight"]], dim=0))
+            self.shared_down = runtime.matrix(tensors["shared.down_proj.weight"])
         names = range(self.num_experts)
         self.gate_up_weight = runtime.matrix(torch.stack([
             torch.cat([tensors[f"experts.{e}.gate_proj.weight"], tensors[f"experts.{e}.up_proj.weight"]], dim=0)
@@ -70,7 +115,18 @@ class RoutedMLP(FeedForward):
         logits = ops.project(x, self.router_weight, ctx.status, out_dtype=torch.float32)   # [T, E], or partial sums
         expert_ids = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
         weights = torch.empty((tokens, top_k), dtype=torch.float32, device=device)
-        ops.router_topk(logits, top_k, self.score, self.renormalise, expert_ids, weights)
+        ops.router_topk(logits, top_k, self.score, self.renormalise, expert_ids, weights, self.num_outputs,
+                        self.correction, self.groups)
+        addend_gate = None
+        if self.shared_size:
+            if add is not None:
+                raise ValueError("a routed feed-forward with a shared expert takes no other addend")
+            gate_up = ops.project(x, self.shared_gate_up, ctx.status)
+            inner = torch.empty((tokens, self.shared_size), dtype=dtype, device=device)
+            ops.silu_mul(gate_up, inner)
+            add = ops.project(inner, self.shared_down, ctx.status)      # [T, hidden], or partial sums
+            if self.shared_gated:
+                addend_gate = (logits, self.num_outputs)
         work = torch.empty((3 * experts + 1,), dtype=torch.int32, device=device)
         place = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
         rows = tokens * top_k
@@ -89,5 +145,7 @@ class RoutedMLP(FeedForward):
             y = torch.empty((rows, self.hidden_size), dtype=dtype, device=device)
         ops.moe_gemm(hidden, self.down_weight, offsets, y, ctx.status)
         out = torch.empty((tokens, self.hidden_size), dtype=torch.float32, device=device)
-        ops.moe_combine(y, expert_ids, place, weights, not self.weight_on_input, add, out, experts)
+        ops.moe_combine(y, expert_ids, place, weights, not self.weight_on_input, add, out, experts,
+                        identity_input=x if self.num_identity else None, num_identity=self.num_identity,
+                        addend_gate=addend_gate)
         return out

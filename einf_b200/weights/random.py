@@ -62,6 +62,10 @@ def random_tensors(
             values = 1.5 * values - 2.5
         elif spec.role == "near_identity":  # a square matrix that mixes its rows a little
             values = torch.eye(spec.shape[-1], device=device) + 0.2 * values
+        elif spec.role == "small":         # a selection bias well below the scores' spread
+            values = 0.05 * values
+        elif spec.role == "forget_bias":   # a forget gate that mostly keeps: its sigmoid lies near 0.9
+            values = 2.0 + values
         elif spec.role == "depth":         # weights over the depth: mostly the newest result
             values = 0.2 * values / spec.shape[-1]
             values[..., -1] += 1.0

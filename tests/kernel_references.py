@@ -18,8 +18,8 @@ import torch
 _MASK64 = (1 << 64) - 1
 
 
-def embed(tokens, table, residual, status, positions=None, position_table=None):
-    residual.copy_(table[tokens.long()].float())
+def embed(tokens, table, residual, status, positions=None, position_table=None, scale=1.0):
+    residual.copy_(table[tokens.long()].float() * scale)
     if position_table is not None:
         residual.add_(position_table[positions.long()].float())
 
@@ -97,7 +97,7 @@ def project(x, weight, status, out_dtype=None, allow_partial=True):
 
 
 def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window, status,
-                            chunk=None, softcap=None, keep_first=0, values_in_keys=None):
+                            chunk=None, softcap=None, keep_first=0, values_in_keys=None, sink=None):
     tokens, num_heads, head_size = q.shape
     _, num_kv_heads, page_size, _ = k_cache.shape
     groups = num_heads // num_kv_heads
@@ -119,7 +119,9 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, posi
         scores = torch.einsum("hd,nhd->hn", q[t].float(), k) * scale
         if softcap:
             scores = softcap * torch.tanh(scores / softcap)
-        probabilities = torch.softmax(scores, dim=-1)
+        if sink is not None:        # one more column in the denominator, with no value
+            scores = torch.cat([scores, sink.float()[:, None]], dim=1)
+        probabilities = torch.softmax(scores, dim=-1)[:, :keys.shape[0]]
         out[t] = torch.einsum("hn,nhd->hd", probabilities, v).to(out.dtype)
 
 
@@ -170,18 +172,35 @@ def _rotate(x, positions, inv_freq, interleaved):
 
 def qkv_norm_store(qkv, bias, slots, q_out, k_cache, v_cache, num_heads, num_kv_heads, key_size, value_size,
                    unit_eps, status, positions=None, inv_freq=None, interleaved=False, value_mix=None,
-                   shared_values=None, mix=None):
+                   shared_values=None, mix=None, q_norm_weight=None, k_norm_weight=None, norm_rows=False,
+                   values_from_keys=False):
     values = _summed(qkv)
     tokens = values.shape[0]
     if bias is not None:
         values = values + bias
-    q, k, v = values.split([num_heads * key_size, num_kv_heads * key_size, num_kv_heads * value_size], dim=-1)
+    if values_from_keys:
+        q, k = values.split([num_heads * key_size, num_kv_heads * key_size], dim=-1)
+        v = k
+    else:
+        q, k, v = values.split([num_heads * key_size, num_kv_heads * key_size, num_kv_heads * value_size], dim=-1)
+    v = v.reshape(tokens, num_kv_heads, value_size)
+    if unit_eps is not None and norm_rows:          # one root mean square for all heads of a row
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + unit_eps)
+        if num_kv_heads:
+            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + unit_eps)
+        if q_norm_weight is not None:
+            q = q * q_norm_weight
+        if k_norm_weight is not None and num_kv_heads:
+            k = k * k_norm_weight
     q = q.reshape(tokens, num_heads, key_size)
     k = k.reshape(tokens, num_kv_heads, key_size)
-    v = v.reshape(tokens, num_kv_heads, value_size)
-    if unit_eps is not None:
+    if unit_eps is not None and not norm_rows:
         q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + unit_eps)
         k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + unit_eps)
+        if q_norm_weight is not None:
+            q = q * q_norm_weight
+        if k_norm_weight is not None:
+            k = k * k_norm_weight
     if inv_freq is not None and inv_freq.shape[0]:
         q = _rotate(q, positions, inv_freq, interleaved)
         k = _rotate(k, positions, inv_freq, interleaved)
@@ -229,10 +248,24 @@ def per_head_project(x, weight, out):
     out.copy_(torch.einsum("thi,hoi->tho", x.float(), weight.float()).to(out.dtype))
 
 
-def router_topk(logits, top_k, score, renormalise, expert_ids, weights):
+def router_topk(logits, top_k, score, renormalise, expert_ids, weights, num_experts=None, correction=None,
+                groups=None):
     z = _summed(logits)
-    order = torch.sort(z, dim=-1, descending=True, stable=True).indices[:, :top_k]
+    if num_experts is not None:
+        z = z[:, :num_experts]
     scores = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, dim=-1)
+    # without a correction the choice goes by the logits themselves (the scores are monotone in them)
+    choice = z if correction is None else scores + correction
+    if groups is not None:
+        count, keep = groups
+        tokens, experts = choice.shape
+        best = choice.reshape(tokens, count, experts // count).max(dim=-1).values
+        kept = torch.sort(best, dim=-1, descending=True, stable=True).indices[:, :keep]
+        allowed = torch.zeros(tokens, count, dtype=torch.bool, device=z.device)
+        allowed.scatter_(1, kept, True)
+        allowed = allowed.repeat_interleave(experts // count, dim=1)
+        choice = torch.where(allowed, choice, torch.full_like(choice, -torch.inf))
+    order = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :top_k]
     chosen = torch.gather(scores, 1, order)
     if renormalise:
         chosen = chosen / chosen.sum(-1, keepdim=True)
@@ -243,8 +276,8 @@ def router_topk(logits, top_k, score, renormalise, expert_ids, weights):
 def moe_dispatch(x, expert_ids, weights, num_experts, scale_rows, work, place, sorted_x):
     tokens, top_k = expert_ids.shape
     flat = expert_ids.reshape(-1).long()
-    order = torch.sort(flat, stable=True).indices          # sorted row -> pair
-    counts = torch.bincount(flat, minlength=num_experts)
+    order = torch.sort(flat, stable=True).indices          # sorted row -> pair; ids beyond the experts come last
+    counts = torch.bincount(flat, minlength=num_experts)[:num_experts]
     offsets = torch.zeros(num_experts + 1, dtype=torch.int32, device=x.device)
     offsets[1:] = counts.cumsum(0).to(torch.int32)
     work[2 * num_experts:] = offsets
@@ -276,17 +309,27 @@ def moe_gemm_splits(rows, experts, n, k):
     return 1
 
 
-def moe_combine(y, expert_ids, place, weights, scale_outputs, addend, out, num_experts):
+def moe_combine(y, expert_ids, place, weights, scale_outputs, addend, out, num_experts, identity_input=None,
+                num_identity=0, addend_gate=None):
     total = torch.zeros_like(out) if addend is None else _summed(addend).clone()
+    if addend_gate is not None:
+        gate, column = addend_gate
+        total = total * torch.sigmoid(_summed(gate)[:, column])[:, None]
     y = _summed(y)
     for j in range(expert_ids.shape[1]):
+        e = expert_ids[:, j]
         term = y[place[:, j].long()]
-        total = total + (weights[:, j, None] * term if scale_outputs else term)
+        term = weights[:, j, None] * term if scale_outputs else term
+        term = torch.where((e < num_experts)[:, None], term, torch.zeros_like(term))
+        if num_identity:
+            through = (e >= num_experts) & (e < num_experts + num_identity)
+            term = term + torch.where(through[:, None], weights[:, j, None] * identity_input.float(), torch.zeros_like(term))
+        total = total + term
     out.copy_(total)
 
 
-def softcap(values, cap):
-    values.copy_(cap * torch.tanh(values / cap))
+def softcap(values, cap, scale=1.0):
+    values.copy_(cap * torch.tanh(values * scale / cap) if cap else values * scale)
 
 
 def conv_silu(x, weight, bias, conv_state, seq_of_token, q_start, state_slots, out, dt_raw=None, dt_bias=None,
@@ -355,6 +398,51 @@ def gated_norm(y, gate, weight, out, parts, eps, gate_first, gate_kind):
     if not gate_first:
         result = result * g
     out.copy_(result.to(out.dtype))
+
+
+def memory_value_columns(vdim):
+    return (vdim + 1 + 3) // 4 * 4
+
+
+def memory_gates(gates, bias, cap, v, top_state, q_start, state_slots, decay, scale, floor, v_wide, heads, vdim):
+    z = _summed(gates) + bias
+    tokens = z.shape[0]
+    log_in = cap * torch.tanh(z[:, :heads] / cap)
+    log_keep = torch.nn.functional.logsigmoid(cap * torch.tanh(z[:, heads:] / cap))
+    for r in range(state_slots.shape[0]):
+        first, last = int(q_start[r]), int(q_start[r + 1])
+        slot = int(state_slots[r])
+        top = top_state[slot].clone() if slot >= 0 else torch.zeros(heads, device=z.device)
+        for t in range(first, last):
+            new_top = torch.maximum(log_keep[t] + top, log_in[t])
+            decay[t] = torch.exp(log_keep[t] + top - new_top)
+            scale[t] = torch.exp(log_in[t] - new_top)
+            floor[t] = torch.exp(-new_top)
+            top = new_top
+        if slot >= 0 and last > first:
+            top_state[slot] = top
+    columns = v_wide.shape[1] // heads
+    wide = torch.zeros(tokens, heads, columns, dtype=torch.float32, device=v.device)
+    wide[:, :, :vdim] = v.float().reshape(tokens, heads, vdim)
+    wide[:, :, vdim] = 1.0
+    v_wide.copy_(wide.reshape(tokens, heads * columns).to(v_wide.dtype))
+
+
+def memory_output(y, floor, gate, weight, out, heads, vdim, query_scale, eps, denominator_eps):
+    tokens = y.shape[0]
+    wide = y.reshape(tokens, heads, -1)
+    below = torch.maximum((query_scale * wide[:, :, vdim]).abs(), floor) + denominator_eps
+    o = query_scale * wide[:, :, :vdim] / below[:, :, None]
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps)
+    out.copy_((o.reshape(tokens, heads * vdim) * weight * torch.sigmoid(gate.float())).to(out.dtype))
+
+
+def norm_join(terms, weights, eps, out, scale=1.0):
+    total = torch.zeros_like(out)
+    for term, weight in zip(terms, weights):
+        t = _summed(term)
+        total = total + weight * (t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps))
+    out.copy_(scale * total)
 
 
 def _gelu_tanh(z):
@@ -551,7 +639,8 @@ _NAMES = (
     "zero_fresh_state", "has_fast_attention", "activation", "qkv_norm_store", "conv_silu", "linear_recurrence",
     "gated_norm", "recurrence_plan", "latent_down_store", "latent_q_store", "per_head_project", "router_topk",
     "moe_dispatch", "moe_gemm", "moe_combine", "softcap", "latent_decode_attention", "latent_decode_splits", "moe_gemm_on_tensor_cores", "moe_gemm_splits",
-    "act_mul", "norm_conv", "stream_tail", "paged_attention_mixed", "gated_scan",
+    "act_mul", "norm_conv", "stream_tail", "paged_attention_mixed", "gated_scan", "memory_gates", "memory_output",
+    "norm_join", "memory_value_columns",
 )
 
 
