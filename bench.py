@@ -722,7 +722,7 @@ def run_kanavik(args) -> dict:
             runner = ModelRunner.from_random(
                 config_from_dict(cfg), 0,
                 EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=pages, max_batch_len=8192,
-                             max_prefill_chunk_len=8192, max_requests=64))
+                             max_prefill_chunk_len=8192, max_requests=64, use_cuda_graphs=not args.no_graphs))
             manager = CacheManager(runner.group_specs(), runner.num_state_slots)
             sampler = Sampler(runner.runtime.device, 64)
             for tokens in {"decode": (), "prefill": (2048,)}.get(args.only, (2048, 8192)):
@@ -1171,6 +1171,285 @@ def bomipel_kernels(peak: dict) -> dict:
     return out
 
 
+def rekodra_sizes(width: int, heads: int, kv_heads: int, size: int, ff: int, vocab: int, window: int) -> dict:
+    """A Rekodra configuration at the layer sizes of a Qwen2 model, eight runs of a layer: a parallel
+    layer (windowed attention beside a matrix memory as wide as the model), two attention layers
+    with a sink that run twice, then the same three again once.  Every layer routes to four of
+    eight experts and four pass-through experts in two groups of which one is kept, beside a
+    shared expert; the four chosen and the shared one together are as wide as the dense feed-forward
+    when all four are real experts."""
+    memory_heads = max(1, heads // 2)
+    parallel = {"type": "parallel", "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": size, "vdim": size, "scale": size ** -0.5,
+                 "mask": {"size": window}},
+        "right": {"heads": memory_heads, "dim": size, "vdim": width // memory_heads, "gate_cap": 15.0}}}
+    attention = {"type": "attention", "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": size, "vdim": size, "scale": size ** -0.5,
+        "rot": {"base": 1000000.0, "dims": size // 2}}}
+    mlp = {"kind": "moe", "expert": {"ff": ff // 5 // 8 * 8},
+           "router": {"experts": 8, "identity": 4, "top": 4, "groups": {"count": 2, "keep": 1}},
+           "shared": {"ff": ff // 5 // 8 * 8}}
+    layers = [dict(layer, mlp=mlp) for layer in (parallel, attention, attention, parallel, attention, attention)]
+    return {"architecture": "Rekodra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 0.5}, "logit_scale": 0.25, "loop": {"start": 1, "stop": 3, "times": 2},
+            "layers": layers}
+
+
+def run_rekodra(args) -> dict:
+    """Prefill and decode throughput of the Rekodra design at the layer sizes of the 0.5B and 1.5B
+    models (random weights, eight runs of a layer), beside Bomipel, the closest of the other
+    designs (windowed attention, routed feed-forwards), and Qwen2, each with eight layers at the
+    same width, heads and vocabulary; then the design's own kernels alone, each beside the like
+    kernel of another path."""
+    import torch
+
+    from einf_b200.cache import CacheManager
+    from einf_b200.config import EngineConfig, config_from_dict
+    from einf_b200.engine import ModelRunner
+    from einf_b200.sampling import Sampler
+
+    peak = peaks()
+    result = {"scenario": "rekodra", "layer_runs": 8, "context": CONTEXT, "window": 1024}
+    shapes = {"0.5b": (896, 4864, 14, 2, 64), "1.5b": (1536, 8960, 12, 2, 128)}
+    if args.only != "all":          # one small workload for a launch list
+        shapes = {"0.5b": shapes["0.5b"]}
+    for name, (width, ff, heads, kv_heads, size) in shapes.items():
+        qwen = dict(SIZES["1.5b"] if name == "1.5b" else QWEN25_05B, num_hidden_layers=8, tie_word_embeddings=True)
+        vocab = qwen["vocab_size"]
+        ours = rekodra_sizes(width, heads, kv_heads, size, ff, vocab, 1024)
+        near = bomipel_sizes(width, heads, kv_heads, size, ff, 8, 2, 96, 32, (384, 768)[name == "1.5b"], 8, vocab, 1024, 4)
+        for arch, cfg in (("rekodra", ours), ("bomipel", near), ("qwen2", qwen)):
+            if arch != "rekodra" and args.only != "all":
+                continue
+            pages = 64 * (CONTEXT // PAGE + 2) + 64
+            runner = ModelRunner.from_random(
+                config_from_dict(cfg), 0,
+                EngineConfig(dtype="bfloat16", block_len=PAGE, num_blocks=pages, max_batch_len=8192,
+                             max_prefill_chunk_len=8192, max_requests=64, use_cuda_graphs=not args.no_graphs))
+            manager = CacheManager(runner.group_specs(), runner.num_state_slots)
+            sampler = Sampler(runner.runtime.device, 64)
+            for tokens in {"decode": (), "prefill": (2048,)}.get(args.only, (2048, 8192)):
+                timed = time_prefill(runner, sampler, manager, tokens, repeats=2 if args.only == "prefill" else 5)
+                result[f"{name}_{arch}_prefill{tokens}_ms"] = round(timed["ms"], 3)
+                result[f"{name}_{arch}_prefill{tokens}_tokens_per_s"] = round(tokens / (timed["ms"] * 1e-3))
+            for batch in {"decode": (args.batch,), "prefill": ()}.get(args.only, (1, 8, 64)):
+                timed = time_decode(runner, sampler, manager, batch, CONTEXT, args.steps, args.warmup,
+                                    min_seconds=0.0 if args.only == "decode" else 0.2)
+                result[f"{name}_{arch}_decode_b{batch}_ms"] = round(timed["ms_per_step"], 3)
+                result[f"{name}_{arch}_decode_b{batch}_tokens_per_s"] = round(timed["tokens_per_s"], 1)
+                result[f"{name}_{arch}_decode_b{batch}_launches_per_step"] = timed["launches"] // max(1, args.steps)
+            del runner, manager, sampler
+            torch.cuda.empty_cache()
+    if args.only not in ("decode", "prefill"):
+        result["kernels"] = rekodra_kernels(peak)
+    return result
+
+
+def rekodra_kernels(peak: dict) -> dict:
+    """The design's kernels alone (microseconds per launch in a CUDA graph of launches on rotating
+    buffers larger than the L2) with the bytes or flops each must move, each beside the like kernel of
+    another path: attention with a sink beside plain causal attention, the store kernel with norms
+    over whole rows and values taken from the keys beside the rotary store of Qwen2, the matrix
+    memory (gates, recurrence on the widened values, output) beside lightning attention's
+    recurrence and gated norm, the normed join beside the residual norm, the router with a
+    correction and groups and the combine with pass-through experts and a gated shared expert
+    beside the plain ones."""
+    import torch
+
+    from einf_b200 import ops
+
+    device = torch.device("cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    out: dict = {}
+    gbs, tflops = peak["hbm_gbs"], peak["bf16_tflops"]
+    turn = [0]
+
+    def rate(key, us, nbytes=0, flops=0):
+        out[key + "_us"] = round(us, 1)
+        if nbytes:
+            out[key + "_hbm_frac"] = round(nbytes / us / 1e3 / gbs, 3)
+        if flops:
+            out[key + "_flops_frac"] = round(flops / us / 1e6 / tflops, 4)
+
+    for name, width, heads, kv_heads, size in (("0.5b", 896, 14, 2, 64), ("1.5b", 1536, 12, 2, 128)):
+        ops.ensure_built(list(ops.attention_libraries(size, PAGE)) + ["recurrence", "pointwise", "routed"])
+        sink = torch.randn(heads, device=device)
+        # --- attention over a prompt of 2,048 tokens, with and without a sink
+        tokens = 2048
+        pages, launches = tokens // PAGE, 8
+        k = torch.randn(pages * launches + 4, kv_heads, PAGE, size, device=device).bfloat16()
+        v = torch.randn_like(k)
+        q = torch.randn(tokens, heads, size, device=device).bfloat16()
+        o = torch.empty_like(q)
+        tables = [torch.arange(i * pages, (i + 1) * pages, dtype=torch.int32, device=device).view(1, -1) for i in range(launches)]
+        tiles = torch.tensor([[0, first, 128, first] for first in range(0, tokens, 128)], dtype=torch.int32, device=device)
+
+        def prefill(sink=None):
+            turn[0] += 1
+            ops.paged_prefill_attention(q, k, v, tables[turn[0] % launches], tiles, o, size ** -0.5, None, status,
+                                        cached_before=0, sink=sink)
+
+        flops = 4 * heads * size * tokens * tokens / 2
+        rate(f"{name}_prefill_attention_causal", _graph_time_us(prefill, launches), flops=flops)
+        rate(f"{name}_prefill_attention_sink", _graph_time_us(lambda: prefill(sink), launches), flops=flops)
+        # --- the store kernels on 2,048 and on 8 rows of a product
+        for rows in (2048, 8):
+            slots = torch.arange(rows, dtype=torch.int32, device=device)
+            positions = torch.arange(rows, dtype=torch.int32, device=device)
+            qo = torch.empty(rows, heads, size, device=device).bfloat16()
+            pairs = size // 4
+            inv_freq = (1e6 ** (-torch.arange(pairs, device=device).float() / pairs)).contiguous()
+            full_freq = (1e6 ** (-torch.arange(size // 2, device=device).float() / (size // 2))).contiguous()
+            qk = torch.randn(rows, (heads + kv_heads) * size, device=device).bfloat16()
+            qkv = torch.randn(rows, (heads + 2 * kv_heads) * size, device=device).bfloat16()
+            wq, wk = torch.ones(heads * size, device=device), torch.ones(kv_heads * size, device=device)
+            hq = torch.ones(size, device=device)
+            moved = (2 * heads + 3 * kv_heads) * size * rows * 2
+            rate(f"{name}_store_rows{rows}_row_norm_rotation_values_from_keys", _graph_time_us(
+                lambda: ops.qkv_norm_store(qk, None, slots, qo, k, v, heads, kv_heads, size, size, 1e-6, status,
+                                           positions=positions, inv_freq=inv_freq, q_norm_weight=wq, k_norm_weight=wk,
+                                           norm_rows=True, values_from_keys=True), 8), nbytes=moved)
+            rate(f"{name}_store_rows{rows}_head_norm", _graph_time_us(
+                lambda: ops.qkv_norm_store(qkv, None, slots, qo, k, v, heads, kv_heads, size, size, 1e-6, status,
+                                           q_norm_weight=hq, k_norm_weight=hq), 8), nbytes=moved + kv_heads * size * rows * 2)
+            rate(f"{name}_store_rows{rows}_rotary_qwen2", _graph_time_us(
+                lambda: ops.rope_kv_write(qkv, None, positions, full_freq, slots, qo, k, v, heads, kv_heads, size, status), 8),
+                nbytes=moved + kv_heads * size * rows * 2)
+        del k, v
+        # --- single tokens of 8 and 64 requests at 4,096 tokens, with and without a sink
+        for batch in (8, 64):
+            context = CONTEXT
+            pages = context // PAGE
+            layer_bytes = 2 * batch * context * kv_heads * size * 2
+            launches = max(4, min(12, int(1.5e9 // layer_bytes)))
+            k = torch.randn(pages * batch * launches + 2, kv_heads, PAGE, size, device=device).bfloat16()
+            v = torch.randn_like(k)
+            qd = torch.randn(batch, heads, size, device=device).bfloat16()
+            od = torch.empty_like(qd)
+            dtables = [torch.arange(i * pages * batch, (i + 1) * pages * batch, dtype=torch.int32, device=device).view(batch, pages)
+                       for i in range(launches)]
+            seq = torch.arange(batch, dtype=torch.int32, device=device)
+            positions = torch.full((batch,), context - 1, dtype=torch.int32, device=device)
+
+            def decode(sink=None):
+                turn[0] += 1
+                ops.paged_decode_attention_auto(qd, k, v, dtables[turn[0] % launches], seq, positions, od, size ** -0.5,
+                                                None, status, max_context=context, sink=sink)
+
+            rate(f"{name}_decode_attention_b{batch}_causal", _graph_time_us(decode, launches), nbytes=layer_bytes)
+            rate(f"{name}_decode_attention_b{batch}_sink", _graph_time_us(lambda: decode(sink), launches), nbytes=layer_bytes)
+            del k, v
+        # --- the matrix memory beside lightning attention's recurrence: a prompt, and single tokens
+        m_heads, dim = max(1, heads // 2), size
+        vdim = width // m_heads
+        columns = ops.memory_value_columns(vdim)
+        l_heads, l_dim = heads, size                 # lightning attention at the same layer sizes
+        for what, lengths in (("prompt2048", [2048]), ("decode_b8", [1] * 8), ("decode_b64", [1] * 64)):
+            requests, rows = len(lengths), sum(lengths)
+            starts = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=device)
+            slots = torch.arange(requests, dtype=torch.int32, device=device)
+            row = (m_heads * dim * columns + m_heads + 3) // 4 * 4
+            copies = max(2, min(16, int(3e8 // (requests * row * 4))))
+            states = [torch.zeros(requests, row, device=device) for _ in range(copies)]
+            raw = torch.randn(rows, 2 * m_heads, device=device)
+            bias = torch.randn(2 * m_heads, device=device)
+            proj = (torch.randn(rows, 2 * m_heads * dim + 2 * m_heads * vdim, device=device) * 0.3).bfloat16()
+            keys = m_heads * dim
+            mq, mk = proj[:, :keys], proj[:, keys:2 * keys]
+            mv, mg = proj[:, 2 * keys:2 * keys + m_heads * vdim], proj[:, 2 * keys + m_heads * vdim:]
+            decay, scale, floor = (torch.empty(rows, m_heads, device=device) for _ in range(3))
+            wide = torch.empty(rows, m_heads * columns, device=device).bfloat16()
+            y = torch.empty(rows, m_heads * columns, device=device)
+            weight = torch.ones(m_heads * vdim, device=device)
+            mo = torch.empty(rows, m_heads * vdim, device=device).bfloat16()
+
+            def gates():
+                state = states[turn[0] % copies]
+                ops.memory_gates(raw, bias, 15.0, mv, state[:, m_heads * dim * columns:m_heads * dim * columns + m_heads],
+                                 starts, slots, decay, scale, floor, wide, m_heads, vdim, max_q_len=max(lengths))
+
+            def recurrence():
+                turn[0] += 1
+                state = states[turn[0] % copies][:, :m_heads * dim * columns].view(requests, m_heads, dim, columns)
+                ops.linear_recurrence(mq, mk, wide, state, starts, slots, y, m_heads, m_heads, dim, columns,
+                                      token_decay=decay, token_scale=scale, max_q_len=max(lengths))
+
+            def output():
+                ops.memory_output(y, floor, mg, weight, mo, m_heads, vdim, dim ** -0.5, 1e-6, 1e-6)
+
+            gates()
+            state_bytes = 2 * requests * m_heads * dim * columns * 4
+            moved = state_bytes + rows * (2 * keys + m_heads * columns) * 2 + rows * m_heads * columns * 4
+            rate(f"{name}_memory_gates_{what}", _graph_time_us(gates, 4), nbytes=rows * m_heads * (vdim + columns) * 2)
+            rate(f"{name}_memory_recurrence_{what}", _graph_time_us(recurrence, copies), nbytes=moved,
+                 flops=4 * rows * m_heads * dim * columns)
+            rate(f"{name}_memory_output_{what}", _graph_time_us(output, 4),
+                 nbytes=rows * m_heads * (columns * 4 + 2 * vdim * 2))
+            # lightning attention: the same kernel with one decay a head, and the gated norm behind it
+            lstates = [torch.zeros(requests, l_heads, l_dim, l_dim, device=device) for _ in range(copies)]
+            lq = (torch.randn(rows, l_heads * l_dim, device=device) * 0.1).bfloat16()
+            lv = torch.randn(rows, l_heads * l_dim, device=device).bfloat16()
+            ly = torch.empty(rows, l_heads * l_dim, device=device)
+            lo = torch.empty(rows, l_heads * l_dim, device=device).bfloat16()
+            head_decay = torch.full((l_heads,), 0.99, device=device)
+            lweight = torch.ones(l_heads * l_dim, device=device)
+
+            def lightning():
+                turn[0] += 1
+                ops.linear_recurrence(lq, lq, lv, lstates[turn[0] % copies], starts, slots, ly, l_heads, l_heads, l_dim, l_dim,
+                                      head_decay=head_decay, max_q_len=max(lengths))
+
+            lmoved = 2 * requests * l_heads * l_dim * l_dim * 4 + rows * 3 * l_heads * l_dim * 2 + rows * l_heads * l_dim * 4
+            rate(f"{name}_lightning_recurrence_{what}", _graph_time_us(lightning, copies), nbytes=lmoved,
+                 flops=4 * rows * l_heads * l_dim * l_dim)
+            rate(f"{name}_gated_norm_{what}", _graph_time_us(
+                lambda: ops.gated_norm(ly, lv, lweight, lo, 1, 1e-6, gate_first=False, gate_kind="sigmoid"), 4),
+                nbytes=rows * l_heads * l_dim * 8)
+            del states, lstates
+        # --- the normed join of two branches beside the residual norm; the router and the combine
+        experts, identity, top = 8, 4, 4
+        outputs = experts + identity
+        for rows in (2048, 8):
+            left = torch.randn(4, rows, width, device=device) if rows == 8 else torch.randn(rows, width, device=device).bfloat16()
+            right = torch.randn(4, rows, width, device=device) if rows == 8 else torch.randn(rows, width, device=device).bfloat16()
+            weights = [torch.ones(width, device=device), torch.ones(width, device=device)]
+            joined = torch.empty(rows, width, device=device)
+            residual = torch.randn(rows, width, device=device)
+            normed = torch.empty(rows, width, device=device).bfloat16()
+            in_bytes = sum(t.numel() * t.element_size() for t in (left, right))
+            rate(f"{name}_norm_join_rows{rows}", _graph_time_us(
+                lambda: ops.norm_join([left, right], weights, 1e-6, joined, 0.5), 8), nbytes=in_bytes + rows * width * 4)
+            rate(f"{name}_add_rmsnorm_rows{rows}", _graph_time_us(
+                lambda: ops.add_rmsnorm(left, residual, weights[0], 1e-6, normed, None, status), 8),
+                nbytes=left.numel() * left.element_size() + rows * width * 10)
+            logits = torch.randn(rows, outputs + 1, device=device)
+            correction = torch.randn(outputs, device=device) * 0.05
+            ids = torch.empty(rows, top, dtype=torch.int32, device=device)
+            gate_weights = torch.empty(rows, top, device=device)
+            rate(f"{name}_router_rows{rows}_correction_groups", _graph_time_us(
+                lambda: ops.router_topk(logits, top, "softmax", False, ids, gate_weights, outputs, correction, (2, 1)), 8))
+            rate(f"{name}_router_rows{rows}_plain", _graph_time_us(
+                lambda: ops.router_topk(logits, top, "softmax", False, ids, gate_weights, outputs), 8))
+            x = torch.randn(rows, width, device=device).bfloat16()
+            work = torch.empty(3 * experts + 1, dtype=torch.int32, device=device)
+            place = torch.empty(rows, top, dtype=torch.int32, device=device)
+            sorted_x = torch.empty(rows * top, width, device=device).bfloat16()
+            ops.router_topk(logits, top, "softmax", False, ids, gate_weights, outputs, correction, (2, 1))
+            ops.moe_dispatch(x, ids, gate_weights, experts, False, work, place, sorted_x)
+            yy = torch.randn(rows * top, width, device=device).bfloat16()
+            shared = torch.randn(rows, width, device=device).bfloat16()
+            total = torch.empty(rows, width, device=device)
+            rate(f"{name}_combine_rows{rows}_pass_through_gated_shared", _graph_time_us(
+                lambda: ops.moe_combine(yy, ids, place, gate_weights, True, shared, total, experts, identity_input=x,
+                                        num_identity=identity, addend_gate=(logits, outputs)), 8),
+                nbytes=rows * width * (top * 2 + 2 + 2 + 4))
+            rate(f"{name}_combine_rows{rows}_plain", _graph_time_us(
+                lambda: ops.moe_combine(yy, ids, place, gate_weights, True, shared, total, experts), 8),
+                nbytes=rows * width * (top * 2 + 2 + 4))
+    out["status"] = int(status)
+    return out
+
+
 def run_decode_sizes(args) -> dict:
     """Decode at the 1.5B and 7B sizes of the family (batch 8 and 64, context 4,096) with the
     fraction of the HBM roofline each step reaches: at these sizes a step's kernels are long
@@ -1507,7 +1786,7 @@ def main() -> int:
                         help="leave the 1.5B and 7B workloads out of `points` (they take about a minute)")
     parser.add_argument("--lookahead", type=int, default=8,
                         help="EngineConfig.decode_lookahead of the end-to-end run: decode steps per report to the host")
-    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention", "prefill-sizes", "tepavik", "bomipel", "bomipel-kernels", "kanavik", "kanavik-kernels"), default="default",
+    parser.add_argument("--scenario", choices=("default", "1.5b-mixed", "7b-preempt", "decode-sizes", "decode-contexts", "sampling", "prefill-attention", "decode-attention", "prefill-sizes", "tepavik", "bomipel", "bomipel-kernels", "kanavik", "kanavik-kernels", "rekodra", "rekodra-kernels"), default="default",
                         help="other workloads of the baseline: a mixed step at 1.5B sizes, decoding under "
                              "cache pressure at 7B sizes, decode rooflines at 1.5B and 7B sizes; each prints "
                              "its own JSON line")
@@ -1545,6 +1824,8 @@ def main() -> int:
         return 0
     scenarios = {"1.5b-mixed": run_mixed_15b, "7b-preempt": run_preempt_7b, "decode-sizes": run_decode_sizes, "decode-contexts": run_decode_contexts, "decode-attention": run_decode_attention, "prefill-sizes": run_prefill_sizes, "tepavik": run_tepavik, "bomipel": run_bomipel, "kanavik": run_kanavik,
                  "kanavik-kernels": lambda args: {"scenario": "kanavik-kernels", "kernels": kanavik_kernels(peaks())},
+                 "rekodra": run_rekodra,
+                 "rekodra-kernels": lambda args: {"scenario": "rekodra-kernels", "kernels": rekodra_kernels(peaks())},
                  "bomipel-kernels": lambda args: {"scenario": "bomipel-kernels", "kernels": bomipel_kernels(peaks())},
                  "sampling": run_sampling, "prefill-attention": run_prefill_attention}
     if args.scenario in scenarios:

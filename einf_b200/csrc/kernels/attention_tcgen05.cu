@@ -365,6 +365,7 @@ struct TcAttentionParams {
   int keep_first;           // with a window: the first that many positions of the sequence stay visible (0: none)
   int chunk;                // chunked mask: a row sees only the keys of its own block of this many positions (0: off)
   float scale, softcap;     // scores are multiplied by scale; with a cap z they become z * tanh(score / z)
+  const float* sink;        // [heads] or null: exp(sink[h]) joins the denominator of head h, with no key and no value
 };
 
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -849,7 +850,9 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
     const float m_all = fmaxf(m_mine, m_other);
     const float f_mine = m_mine == -INFINITY ? 0.f : fast_exp2(m_mine - m_all);
     const float f_other = m_other == -INFINITY ? 0.f : fast_exp2(m_other - m_all);
-    const float l_all = (have ? l_run : 0.f) * f_mine + l_other * f_other;
+    float l_all = (have ? l_run : 0.f) * f_mine + l_other * f_other;
+    // the sink's term, once per row: here when this CTA has all of the row's keys, else at the cluster's merge
+    if (p.sink && csize == 1 && m_all != -INFINITY) l_all += exp2f(p.sink[head] * 1.4426950408889634f - m_all);
     const float* take = xchg_o + (size_t)((g ^ 1) * 128 + r) * (kDimsHere + 1);
     // for a cluster: this CTA's share (sums of both warpgroups, not yet divided), after the exchange area
     float* part_o = reinterpret_cast<float*>(gbase + kShareOff);
@@ -913,6 +916,7 @@ paged_prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q
 #pragma unroll
       for (int offset = 4; offset >= 1; offset >>= 1) l += __shfl_xor_sync(0xffffffffu, l, offset);
       l = __shfl_sync(0xffffffffu, l, 0);
+      if (p.sink && m != -INFINITY) l += exp2f(p.sink[head] * 1.4426950408889634f - m);
       const float inv = l > 0.f ? 1.f / l : 0.f;
       float o[D / 32];
 #pragma unroll
@@ -983,6 +987,7 @@ struct TcDecodeParams {
   int keep_first;           // see TcAttentionParams
   int chunk;                // see TcAttentionParams
   float scale, softcap;
+  const float* sink;        // see TcAttentionParams
   // A token's keys split over `splits` clusters, which meet in global memory: every cluster writes its
   // unnormalised share [16 heads][D + 2] (the accumulator, then maximum and sum) to split_out, every
   // CTA counts itself in split_count, and the CTA that finds itself the last adds the shares up.
@@ -1377,6 +1382,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
       m = m_new;
     }
     if (!kSplit) {
+      if (p.sink && m != -INFINITY) l += exp2f(p.sink[first_head + row] * 1.4426950408889634f - m);
       p.out[(token_heads + first_head + row) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     } else {
       float* share = p.split_out + (((size_t)pair * p.splits + split) * kDecHeads + row) * (D + 2);
@@ -1428,6 +1434,7 @@ paged_decode_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
         l += lc[c] * f;
         o += oc[c] * f;
       }
+      if (p.sink && m != -INFINITY) l += exp2f(p.sink[first_head + row] * 1.4426950408889634f - m);
       p.out[(token_heads + first_head + row) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     }
   }
@@ -1523,7 +1530,7 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
                                                     void* out, int num_tokens, int num_heads, int num_kv_heads,
                                                     int page_size, int num_pages, int table_width, float scale,
                                                     int window, int keep_first, int chunk, float softcap, int cluster,
-                                                    int* status, cudaStream_t stream) {
+                                                    const float* sink, int* status, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   if (cluster < 1 || cluster > 8) return (int)cudaErrorInvalidValue;
   if (keep_first < 0 || (keep_first > 0 && window > 0 && cluster != 1)) return (int)cudaErrorInvalidValue;
@@ -1556,6 +1563,7 @@ extern "C" int einf_paged_prefill_attention_tcgen05(const void* q, const void* k
   p.chunk = chunk;
   p.scale = scale;
   p.softcap = softcap;
+  p.sink = sink;
   cudaError_t e = cudaFuncSetAttribute(paged_prefill_attention_tcgen05_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return (int)e;
@@ -1623,8 +1631,8 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
                                                    int num_tokens, int num_heads, int num_kv_heads, int page_size,
                                                    int num_pages, int table_width, float scale, int window,
                                                    int keep_first, int chunk, float softcap, int cluster, int splits,
-                                                   float* split_out, int* split_count, int* status,
-                                                   cudaStream_t stream) {
+                                                   float* split_out, int* split_count, const float* sink,
+                                                   int* status, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (cluster < 1 || cluster > kDecMaxCluster) return (int)cudaErrorInvalidValue;
   if (splits < 1 || splits > kDecMaxSplits || (splits > 1 && (!split_out || !split_count))) return (int)cudaErrorInvalidValue;
@@ -1658,6 +1666,7 @@ extern "C" int einf_paged_decode_attention_tcgen05(const void* q, const void* k_
   p.chunk = chunk;
   p.scale = scale;
   p.softcap = softcap;
+  p.sink = sink;
   p.splits = splits;
   p.split_out = split_out;
   p.split_count = split_count;

@@ -898,7 +898,11 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
                                       int rotary_pairs, int interleaved, int value_mix,
                                       float* __restrict__ shared_values, const void* __restrict__ mix, int mix_dtype,
                                       const float* __restrict__ q_weight, const float* __restrict__ k_weight,
-                                      int values_from_keys, int* status) {
+                                      int values_from_keys, int token_blocks, int* status) {
+  // token_blocks: a CTA is one token, a warp per head of its row (at most 32); the heads of a section
+  // then share their sums of squares through shared memory instead of each adding up the whole section
+  __shared__ float head_squares[32];
+  __shared__ float pair_cos[128], pair_sin[128];      // token_blocks: the token's angles, made once for all heads
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -913,6 +917,7 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
   int size, base;
   T* dst;
   bool unit = normalise != 0;
+  bool live = true;                   // false: a key or value head of a token that is not cached
   const float* weight = nullptr;     // the norm's weight for this head, indexed by the dimension
   int section = 0, section_size = 0;  // normalise 2: the part of the row whose root mean square counts
   if (item < num_heads) {
@@ -923,12 +928,19 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
     section_size = num_heads * key_size;
   } else {
     const int slot = slots ? slots[t] : -1;
-    if (slot < 0) return;
-    const int page = slot / page_size, offset = slot - page * page_size;
-    if (page >= num_pages) {
-      if (lane == 0) atomicOr(status, kStatusBadPage);
-      return;
+    int page = 0, offset = 0;
+    if (slot < 0) {
+      live = false;
+    } else {
+      page = slot / page_size;
+      offset = slot - page * page_size;
+      if (page >= num_pages) {
+        if (lane == 0) atomicOr(status, kStatusBadPage);
+        live = false;
+        page = 0;
+      }
     }
+    if (!live && !token_blocks) return;      // a warp of a token's CTA stays for the CTA's barrier
     if (item < num_heads + num_kv_heads) {
       const int head = item - num_heads;
       size = key_size;
@@ -963,7 +975,23 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
     }
   }
   float factor = 1.f;
-  if (unit && normalise == 2) {
+  if (token_blocks) {
+    const float mine = warp_sum(ss);
+    if (lane == 0) head_squares[item] = mine;
+    if (rotary_pairs > 0) {
+      const float pos = (float)positions[t];
+      for (int i = threadIdx.x; i < rotary_pairs; i += blockDim.x) sincosf(pos * inv_freq[i], &pair_sin[i], &pair_cos[i]);
+    }
+    __syncthreads();
+    if (!live) return;
+    if (unit) {
+      // the section's heads in order: the same sum in every warp of the section
+      const int head0 = section == 0 ? 0 : num_heads, count = section == 0 ? num_heads : num_kv_heads;
+      float all = 0.f;
+      for (int i = 0; i < count; ++i) all += head_squares[head0 + i];
+      factor = rsqrtf(all / (float)section_size + eps);
+    }
+  } else if (unit && normalise == 2) {
     // every warp of the section adds up the same squares in the same order
     const TIn* whole = qkv + (size_t)t * width + section;
     float all = 0.f;
@@ -1002,7 +1030,12 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
         if (bias) w += bias[base + other];
         if (weight) w *= factor * weight[other];
         float sn, cs;
-        sincosf(pos * inv_freq[pair], &sn, &cs);
+        if (token_blocks) {
+          sn = pair_sin[pair];
+          cs = pair_cos[pair];
+        } else {
+          sincosf(pos * inv_freq[pair], &sn, &cs);
+        }
         v[i] = leads ? v[i] * cs - w * sn : v[i] * cs + w * sn;
       }
     }
@@ -1038,8 +1071,9 @@ __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ b
 
 // Several branches' outputs joined after a norm each: out = scale * sum_i w_i * x_i / rms(x_i), row
 // by row in 32-bit, the root mean square over the row with eps inside the root.  A term may be the
-// partial sums of a split-K product.  One CTA per row; the row's terms are summed twice from
-// global memory (the second read comes from the cache) rather than kept, so any width goes.
+// partial sums of a split-K product.  One CTA per row.  A row of up to kJoinKeep elements a thread
+// stays in registers between the sums of squares and the output; a wider one is summed twice from
+// global memory (the second read comes from the cache), so any width goes.
 struct JoinTerm {
   const void* x; int dtype; int splits; long long stride; const float* weight;
 };
@@ -1053,6 +1087,8 @@ __device__ __forceinline__ float join_value(const JoinTerm& term, size_t at) {
   return to_float(((const __nv_bfloat16*)term.x)[at]);
 }
 
+constexpr int kJoinKeep = 8;
+
 __global__ void norm_join_kernel(const __grid_constant__ JoinArgs a, float eps, float scale, float* __restrict__ out,
                                  int width) {
   __shared__ float scratch[33];
@@ -1060,6 +1096,33 @@ __global__ void norm_join_kernel(const __grid_constant__ JoinArgs a, float eps, 
   pdl_wait();
   const size_t row = (size_t)blockIdx.x * width;
   float factor[4];
+  if (width <= (int)blockDim.x * kJoinKeep) {
+    float total[kJoinKeep];
+#pragma unroll
+    for (int j = 0; j < kJoinKeep; ++j) total[j] = 0.f;
+    for (int i = 0; i < a.terms; ++i) {
+      float x[kJoinKeep];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < kJoinKeep; ++j) {
+        const int d = threadIdx.x + j * blockDim.x;
+        x[j] = d < width ? join_value(a.term[i], row + d) : 0.f;
+        ss += x[j] * x[j];
+      }
+      const float f = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+#pragma unroll
+      for (int j = 0; j < kJoinKeep; ++j) {
+        const int d = threadIdx.x + j * blockDim.x;
+        if (d < width) total[j] += a.term[i].weight[d] * (x[j] * f);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kJoinKeep; ++j) {
+      const int d = threadIdx.x + j * blockDim.x;
+      if (d < width) out[row + d] = scale * total[j];
+    }
+    return;
+  }
   for (int i = 0; i < a.terms; ++i) {
     float ss = 0.f;
     for (int d = threadIdx.x; d < width; d += blockDim.x) {
@@ -1391,6 +1454,8 @@ extern "C" int einf_qkv_norm_store(const void* qkv, int in_dtype, int splits, lo
                                    const float* k_weight, int values_from_keys, int* status,
                                    cudaStream_t stream) {
   if (num_tokens == 0) return 0;
+  // norms over whole rows: a CTA per token where its heads fit one (a warp each)
+  const int token_blocks = normalise == 2 && num_heads + 2 * num_kv_heads <= 32 ? 1 : 0;
   if (normalise < 0 || normalise > 2 || ((q_weight || k_weight) && !normalise)) return (int)cudaErrorInvalidValue;
   if (values_from_keys && (value_size != key_size || value_mix)) return (int)cudaErrorInvalidValue;
   if (rotary_pairs < 0 || 2 * rotary_pairs > key_size || (rotary_pairs > 0 && (!positions || !inv_freq)))
@@ -1399,8 +1464,8 @@ extern "C" int einf_qkv_norm_store(const void* qkv, int in_dtype, int splits, lo
   if (key_size > 256 || value_size > 256 || key_size <= 0 || (num_kv_heads > 0 && value_size <= 0))
     return (int)cudaErrorInvalidValue;
   const long long warps = (long long)num_tokens * (num_heads + 2 * num_kv_heads);
-  const int threads = 128;
-  const long long blocks = (warps * 32 + threads - 1) / threads;
+  const int threads = token_blocks ? 32 * (num_heads + 2 * num_kv_heads) : 128;
+  const long long blocks = token_blocks ? num_tokens : (warps * 32 + threads - 1) / threads;
   if (blocks >= (1ll << 31)) return (int)cudaErrorInvalidValue;
   EINF_DISPATCH_2(in_dtype, TIn, {
     EINF_DISPATCH_2(dtype, T, {
@@ -1408,7 +1473,7 @@ extern "C" int einf_qkv_norm_store(const void* qkv, int in_dtype, int splits, lo
                              (size_t)split_stride, bias, slots, (T*)q_out, (T*)k_cache, (T*)v_cache, num_tokens,
                              num_heads, num_kv_heads, key_size, value_size, normalise, eps, page_size, num_pages,
                              positions, inv_freq, rotary_pairs, interleaved, value_mix, shared_values, mix, mix_dtype,
-                             q_weight, k_weight, values_from_keys, status);
+                             q_weight, k_weight, values_from_keys, token_blocks, status);
     })
   })
 }

@@ -532,16 +532,22 @@ __global__ void gated_norm_kernel(const float* __restrict__ y, const T* __restri
 // sums), m the running maximum that lives in top_state[slot * top_stride + head] (zero after a
 // fresh start; a request without a slot starts from zero and stores nothing).  decay and scale are
 // what the linear recurrence multiplies its state and its input by; they never exceed one.
-// One CTA per request in four phases: the capped logarithms of all its tokens side by side (left
-// in `scale` and `decay`), the maxima by one thread per head (two dependent operations a token, left
-// in `floor`), the three exponentials of all tokens side by side, and the values widened for the
-// recurrence: v_wide[t, h] = [v[t, h] | 1 | 0 ...] of `columns` elements, so that the memory's
-// normaliser (the same recurrence on the keys alone) is one more column of its state.
+// The CTAs (x, request) of a request each widen the values of a share of its tokens for the
+// recurrence, v_wide[t, h] = [v[t, h] | 1 | 0 ...] of `columns` elements, so that the memory's
+// normaliser (the same recurrence on the keys alone) is one more column of its state.  CTA 0 of
+// the request also makes the gates: the capped logarithms of all its tokens side by side (left in
+// `scale` and `decay`), then a warp per head walks the maxima.  A step m -> max(m + f, i) is a pair
+// (f, i), and two steps in a row are the pair (f1 + f2, max(i1 + f2, i2)): every lane folds a run
+// of tokens into one pair, a scan over the warp's 32 pairs gives every lane the maximum its run
+// starts from, and the lane walks its run again, now with the exponentials.  The maximum only
+// sets the scale that state, normaliser and floor share, so the order of these sums moves no result
+// beyond the rounding of that scale.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+constexpr int kGateBatch = 8;      // tokens whose logarithms a lane fetches before it walks them
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 memory_gates_kernel(const float* __restrict__ gates, int splits, size_t split_stride, const float* __restrict__ bias,
                     float cap, const T* __restrict__ v, long long v_stride, float* __restrict__ top_state,
                     long long top_stride, int num_slots, const int* __restrict__ q_start,
@@ -549,14 +555,47 @@ memory_gates_kernel(const float* __restrict__ gates, int splits, size_t split_st
                     float* __restrict__ floor, T* __restrict__ v_wide, int heads, int vdim, int columns) {
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.x;
+  const int r = blockIdx.y;
   const int first = q_start[r], last = q_start[r + 1];
   const int count = last - first;
   if (count <= 0) return;
+  {
+    // this CTA's share of the request's tokens, widened
+    const int per = (count + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int t0 = first + (int)blockIdx.x * per, t1 = min(last, t0 + per);
+    const int wide = heads * columns;
+    for (long long i = threadIdx.x; i < (long long)max(0, t1 - t0) * wide; i += blockDim.x) {
+      const int t = t0 + (int)(i / wide), c = (int)(i % wide);
+      const int h = c / columns, d = c - h * columns;
+      T value = from_float<T>(d == vdim ? 1.f : 0.f);
+      if (d < vdim) value = v[(long long)t * v_stride + h * vdim + d];
+      v_wide[(size_t)t * wide + c] = value;
+    }
+  }
+  if (blockIdx.x != 0) return;
   const int slot = state_slots[r];
   const bool kept = slot >= 0 && slot < num_slots;
   const float inv_cap = 1.f / cap;
   const int width = 2 * heads;
+  if (count == 1) {
+    // a single token (decoding): a thread per head, nothing passes through memory on the way
+    for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+      float zi = bias[h], zf = bias[heads + h];
+      for (int s = 0; s < splits; ++s) {
+        zi += gates[(size_t)s * split_stride + (size_t)first * width + h];
+        zf += gates[(size_t)s * split_stride + (size_t)first * width + heads + h];
+      }
+      const float log_in = cap * tanhf(zi * inv_cap), log_keep = log_sigmoid_f(cap * tanhf(zf * inv_cap));
+      const float m = kept ? top_state[(long long)slot * top_stride + h] : 0.f;
+      const float m_new = fmaxf(log_keep + m, log_in);
+      const size_t at = (size_t)first * heads + h;
+      decay[at] = expf(log_keep + m - m_new);
+      scale[at] = expf(log_in - m_new);
+      floor[at] = expf(-m_new);
+      if (kept) top_state[(long long)slot * top_stride + h] = m_new;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < count * heads; i += blockDim.x) {
     const int t = first + i / heads, h = i % heads;
     float zi = bias[h], zf = bias[heads + h];
@@ -568,39 +607,61 @@ memory_gates_kernel(const float* __restrict__ gates, int splits, size_t split_st
     decay[(size_t)t * heads + h] = log_sigmoid_f(cap * tanhf(zf * inv_cap));
   }
   __syncthreads();
-  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
-    float m = kept ? top_state[(long long)slot * top_stride + h] : 0.f;
-    for (int t = first; t < last; ++t) {
-      m = fmaxf(decay[(size_t)t * heads + h] + m, scale[(size_t)t * heads + h]);
-      floor[(size_t)t * heads + h] = m;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int run = (count + 31) / 32;
+  const int run_first = min(last, first + lane * run), run_last = min(last, run_first + run);
+  for (int h = warp; h < heads; h += (int)(blockDim.x >> 5)) {
+    // this lane's run of tokens as one step (kGateBatch tokens' loads in flight at a time)
+    float add = 0.f, least = -INFINITY;
+    for (int t0 = run_first; t0 < run_last; t0 += kGateBatch) {
+      float log_keep[kGateBatch], log_in[kGateBatch];
+#pragma unroll
+      for (int u = 0; u < kGateBatch; ++u) {
+        const bool in = t0 + u < run_last;
+        log_keep[u] = in ? decay[(size_t)(t0 + u) * heads + h] : 0.f;
+        log_in[u] = in ? scale[(size_t)(t0 + u) * heads + h] : -INFINITY;
+      }
+#pragma unroll
+      for (int u = 0; u < kGateBatch; ++u) {      // a token beyond the run is the step that changes nothing
+        add += log_keep[u];
+        least = fmaxf(least + log_keep[u], log_in[u]);
+      }
     }
-  }
-  __syncthreads();
-  // the maximum before a token: the one of the token ahead of it, or the slot's (still unchanged)
-  for (int i = threadIdx.x; i < count * heads; i += blockDim.x) {
-    const int t = first + i / heads, h = i % heads;
-    const size_t at = (size_t)t * heads + h;
-    const float before = t > first ? floor[at - heads] : (kept ? top_state[(long long)slot * top_stride + h] : 0.f);
-    const float m = floor[at], log_keep = decay[at], log_in = scale[at];
-    decay[at] = expf(log_keep + before - m);
-    scale[at] = expf(log_in - m);
-  }
-  __syncthreads();
-  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
-    const float m = floor[(size_t)(last - 1) * heads + h];
-    if (kept) top_state[(long long)slot * top_stride + h] = m;
-  }
-  for (int i = threadIdx.x; i < count * heads; i += blockDim.x) {
-    const size_t at = (size_t)(first + i / heads) * heads + i % heads;
-    floor[at] = expf(-floor[at]);
-  }
-  const int wide = heads * columns;
-  for (long long i = threadIdx.x; i < (long long)count * wide; i += blockDim.x) {
-    const int t = first + (int)(i / wide), c = (int)(i % wide);
-    const int h = c / columns, d = c - h * columns;
-    T value = from_float<T>(d == vdim ? 1.f : 0.f);
-    if (d < vdim) value = v[(long long)t * v_stride + h * vdim + d];
-    v_wide[(size_t)t * wide + c] = value;
+    // the steps of lanes 0 .. lane in a row
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float add_before = __shfl_up_sync(0xffffffffu, add, o);
+      const float least_before = __shfl_up_sync(0xffffffffu, least, o);
+      if (lane >= o) {
+        least = fmaxf(least_before + add, least);
+        add += add_before;
+      }
+    }
+    const float start = kept ? top_state[(long long)slot * top_stride + h] : 0.f;
+    const float after = fmaxf(start + add, least);           // the maximum behind this lane's run
+    float m = __shfl_up_sync(0xffffffffu, after, 1);
+    if (lane == 0) m = start;
+    for (int t0 = run_first; t0 < run_last; t0 += kGateBatch) {
+      float log_keep[kGateBatch], log_in[kGateBatch];
+#pragma unroll
+      for (int u = 0; u < kGateBatch; ++u) {
+        const bool in = t0 + u < run_last;
+        log_keep[u] = in ? decay[(size_t)(t0 + u) * heads + h] : 0.f;
+        log_in[u] = in ? scale[(size_t)(t0 + u) * heads + h] : -INFINITY;
+      }
+#pragma unroll
+      for (int u = 0; u < kGateBatch; ++u) {
+        if (t0 + u >= run_last) break;
+        const size_t at = (size_t)(t0 + u) * heads + h;
+        const float m_new = fmaxf(log_keep[u] + m, log_in[u]);
+        decay[at] = expf(log_keep[u] + m - m_new);
+        scale[at] = expf(log_in[u] - m_new);
+        floor[at] = expf(-m_new);
+        m = m_new;
+      }
+    }
+    const float end = __shfl_sync(0xffffffffu, after, 31);
+    if (lane == 0 && kept) top_state[(long long)slot * top_stride + h] = end;
   }
 }
 
@@ -921,11 +982,17 @@ extern "C" int einf_memory_gates(const float* gates, int splits, long long split
                                  const void* v, int dtype, long long v_stride, float* top_state, long long top_stride,
                                  int num_slots, const int* q_start, const int* state_slots, int num_requests,
                                  float* decay, float* scale, float* floor, void* v_wide, int num_tokens, int heads,
-                                 int vdim, int columns, cudaStream_t stream) {
+                                 int vdim, int columns, int longest, cudaStream_t stream) {
   if (num_requests == 0 || num_tokens == 0) return 0;
-  if (heads <= 0 || vdim <= 0 || columns <= vdim || !(cap > 0.f)) return (int)cudaErrorInvalidValue;
+  if (heads <= 0 || vdim <= 0 || columns <= vdim || !(cap > 0.f) || num_requests > 65535)
+    return (int)cudaErrorInvalidValue;
+  // CTAs that share a request's tokens for the widening: about 16 tokens each, up to 128
+  if (longest <= 0) longest = num_tokens;
+  int shares = (longest + 15) / 16;
+  shares = shares < 1 ? 1 : (shares > 128 ? 128 : shares);
+  const dim3 grid(shares, num_requests);
   EINF_DISPATCH_2(dtype, T, {
-    return (int)launch_pdl(memory_gates_kernel<T>, num_requests, 128, 0, stream, gates, splits < 1 ? 1 : splits,
+    return (int)launch_pdl(memory_gates_kernel<T>, grid, dim3(256), 0, stream, gates, splits < 1 ? 1 : splits,
                            (size_t)split_stride, bias, cap, (const T*)v, v_stride, top_state, top_stride, num_slots,
                            q_start, state_slots, decay, scale, floor, (T*)v_wide, heads, vdim, columns);
   })

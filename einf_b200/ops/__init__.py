@@ -1335,6 +1335,7 @@ def memory_gates(
     v_wide: torch.Tensor,
     heads: int,
     vdim: int,
+    max_q_len: Optional[int] = None,
 ) -> None:
     """The exponential gates of a matrix memory, stabilised by a running maximum, in 32-bit.
     ``gates`` float32 ``[tokens, 2 heads]`` (or split-K partial sums of it) holds per head the raw
@@ -1349,7 +1350,8 @@ def memory_gates(
     ``scale``, ``floor``: float32 ``[tokens, heads]``.  The same launch widens the values for the
     recurrence: ``v_wide [tokens, heads * columns]`` (v's dtype) is ``v [tokens, heads * vdim]``
     (columns of a wider matrix are fine) with a column of ones behind every head's values and zeros
-    up to ``columns``."""
+    up to ``columns``.  ``max_q_len``: the longest portion of the step as the host knows it (it sizes the
+    launch; None: all tokens)."""
     tokens = v.shape[0]
     columns = v_wide.shape[1] // max(heads, 1)
     splits, stride = _maybe_split(gates, tokens, 2 * heads, "gates")
@@ -1369,13 +1371,13 @@ def memory_gates(
     fn = _fn(
         "einf_memory_gates",
         [c_void_p, c_int, c_longlong, c_void_p, c_float, c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_int,
-         c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+         c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     )
     _check(
         fn(_dev(gates, "gates"), splits, stride, _dev(bias, "bias"), float(cap), v.data_ptr(), _code(v), _rows_of(v, "v"),
            top_state.data_ptr(), top_state.stride(0), top_state.shape[0], _opt(q_start, "q_start", torch.int32),
            _opt(state_slots, "state_slots", torch.int32), requests, _dev(decay, "decay"), _dev(scale, "scale"),
-           _dev(floor, "floor"), _dev(v_wide, "v_wide"), tokens, heads, vdim, columns, _stream()),
+           _dev(floor, "floor"), _dev(v_wide, "v_wide"), tokens, heads, vdim, columns, int(max_q_len or 0), _stream()),
         "memory_gates",
     )
 
@@ -2094,6 +2096,7 @@ def paged_decode_attention_auto(
     chunk: Optional[int] = None,
     softcap: Optional[float] = None,
     keep_first: int = 0,
+    sink: Optional[torch.Tensor] = None,
 ) -> None:
     """Decode attention by the kernel, cluster size and number of clusters per token that
     ``decode_plan`` picks for this batch; ``max_context`` is the longest context among the
@@ -2107,10 +2110,10 @@ def paged_decode_attention_auto(
     if kernel == "tcgen05":
         paged_decode_attention_tcgen05(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window,
                                        cluster, status, token_list, splits, chunk=chunk, softcap=softcap,
-                                       keep_first=keep_first)
-    elif chunk or softcap or (window and keep_first):
-        raise UnsupportedSize("a chunked mask, a soft cap or kept first positions need the tcgen05 decode kernel "
-                              "(head size 64 or 128)")
+                                       keep_first=keep_first, sink=sink)
+    elif chunk or softcap or (window and keep_first) or sink is not None:
+        raise UnsupportedSize("a chunked mask, a soft cap, kept first positions or a sink need the tcgen05 decode "
+                              "kernel (head size 64 or 128)")
     else:
         paged_decode_attention_cluster(q, k_cache, v_cache, block_table, seq_of_token, positions, out, scale, window,
                                        cluster, status, token_list)
@@ -2197,6 +2200,7 @@ def paged_decode_attention_tcgen05(
     chunk: Optional[int] = None,
     softcap: Optional[float] = None,
     keep_first: int = 0,
+    sink: Optional[torch.Tensor] = None,
 ) -> None:
     """Decode attention on the tcgen05 tensor cores with the keys as the 128-row operand
     (S^T = K Q^T, O^T = V^T P^T), so the tile is full at any number of query heads.  Key splits
@@ -2210,6 +2214,8 @@ def paged_decode_attention_tcgen05(
             f"the tcgen05 attention kernels take head sizes 64 and 128 and pages of 8 to 128 tokens, "
             f"got {head_size} and {page_size}"
         )
+    if sink is not None and (sink.dtype != torch.float32 or sink.shape != (num_heads,)):
+        raise ValueError(f"sink must be float32 [{num_heads}]")
     if token_list is not None:
         tokens = token_list.shape[0]
     if not 1 <= cluster <= 16:
@@ -2223,7 +2229,7 @@ def paged_decode_attention_tcgen05(
     fn = _fn(
         "einf_paged_decode_attention_tcgen05",
         [c_void_p] * 8 + [c_int] * 6 + [c_float, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
-         c_void_p],
+         c_void_p, c_void_p],
         f"HEAD_SIZE={head_size}",
     )
     _check(
@@ -2235,7 +2241,7 @@ def paged_decode_attention_tcgen05(
            int(keep_first) if window else 0,
            int(chunk) if chunk else 0, float(softcap) if softcap else 0.0, cluster,
            splits, shares.data_ptr() if splits > 1 else None, counters.data_ptr() if splits > 1 else None,
-           _dev(status, "status"), _stream()),
+           _opt(sink, "sink", torch.float32), _dev(status, "status"), _stream()),
         "paged_decode_attention_tcgen05",
     )
 
@@ -2297,6 +2303,7 @@ def paged_prefill_attention(
     chunk: Optional[int] = None,
     softcap: Optional[float] = None,
     keep_first: int = 0,
+    sink: Optional[torch.Tensor] = None,
 ) -> None:
     """Tensor-core causal attention for prompt portions.  ``q_tiles`` is int32 ``[tiles, 4]``:
     request, first token (packed index), rows (at most ``Q_TILE``), position of the first row.
@@ -2306,9 +2313,11 @@ def paged_prefill_attention(
     ``mma.sync`` kernel.  ``prefill_cluster`` (1 to 8; 0: ``prefill_cluster_size`` of the number of
     row tiles and ``cached_before``, the most tokens that a portion of this step finds in the
     cache, if the caller knows it) is the number of CTAs that share a row tile's keys in the
-    tcgen05 kernel.  ``chunk`` and ``softcap`` (see :func:`paged_attention_generic`) are the tcgen05
+    tcgen05 kernel.  ``chunk``, ``softcap`` and ``sink`` (see :func:`paged_attention_generic`) are the tcgen05
     kernel's alone."""
     tokens, num_heads, head_size, num_pages, num_kv_heads, page_size = _check_fast_attention(q, k_cache, v_cache, out)
+    if sink is not None and (sink.dtype != torch.float32 or sink.shape != (num_heads,)):
+        raise ValueError(f"sink must be float32 [{num_heads}]")
     if q_tiles.dtype != torch.int32 or q_tiles.dim() != 2 or q_tiles.shape[1] != 4:
         raise ValueError("q_tiles must be int32 [tiles, 4]")
     can = has_tcgen05_attention(head_size, page_size)
@@ -2323,7 +2332,7 @@ def paged_prefill_attention(
         fn = _fn(
             "einf_paged_prefill_attention_tcgen05",
             [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 6 + [c_float, c_int, c_int, c_int, c_float, c_int, c_void_p,
-                                                                 c_void_p],
+                                                                 c_void_p, c_void_p],
             f"HEAD_SIZE={head_size}",
         )
         cluster = prefill_cluster
@@ -2340,13 +2349,14 @@ def paged_prefill_attention(
                _dev(out, "out"), tokens, num_heads, num_kv_heads, page_size, num_pages, block_table.shape[1],
                float(scale), int(window) if window else 0, int(keep_first) if window else 0,
                int(chunk) if chunk else 0,
-               float(softcap) if softcap else 0.0, int(cluster), _dev(status, "status"), _stream()),
+               float(softcap) if softcap else 0.0, int(cluster), _opt(sink, "sink", torch.float32),
+               _dev(status, "status"), _stream()),
             "paged_prefill_attention_tcgen05",
         )
         return
-    if chunk or softcap or (window and keep_first):
-        raise UnsupportedSize("a chunked mask, a soft cap or kept first positions need the tcgen05 prefill kernel "
-                              "(head size 64 or 128)")
+    if chunk or softcap or (window and keep_first) or sink is not None:
+        raise UnsupportedSize("a chunked mask, a soft cap, kept first positions or a sink need the tcgen05 prefill "
+                              "kernel (head size 64 or 128)")
     fn = _fn(
         "einf_paged_prefill_attention",
         [c_void_p] * 5 + [c_int, c_void_p] + [c_int] * 5 + [c_float, c_int, c_void_p, c_void_p],

@@ -97,8 +97,7 @@ class PagedAttention(Mixer):
         """A general layer still runs the tcgen05 attention kernels (which know the chunked mask and
         the soft cap) when its keys and values have one size that those kernels take."""
         size = int(spec["head_size"])
-        return dtype == torch.bfloat16 and (spec.get("value_head_size") or size) == size and size in (64, 128) \
-            and not spec.get("sink")
+        return dtype == torch.bfloat16 and (spec.get("value_head_size") or size) == size and size in (64, 128)
 
     @classmethod
     def kernel_libraries(cls, spec, runtime):
@@ -302,13 +301,13 @@ class PagedAttention(Mixer):
                     q, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, out, self.scale,
                     self.window, ctx.status, None if ctx.decode_only else ctx.single_tokens,
                     max_context=ctx.max_context_len, chunk=self.chunk, softcap=self.softcap,
-                    keep_first=self.keep_first,
+                    keep_first=self.keep_first, sink=self.sink,
                 )
             if ctx.q_tiles.shape[0]:
                 ops.paged_prefill_attention(
                     q, cache.k, cache.v, table, ctx.q_tiles, out, self.scale, self.window, ctx.status,
                     cached_before=ctx.max_portion_start, chunk=self.chunk, softcap=self.softcap,
-                    keep_first=self.keep_first,
+                    keep_first=self.keep_first, sink=self.sink,
                 )
             return
         ops.paged_attention_generic(

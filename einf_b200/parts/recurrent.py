@@ -358,7 +358,7 @@ class MatrixMemory(_RecurrentMixer):
         floor = torch.empty_like(decay)
         v_wide = torch.empty((tokens, heads * self.columns), dtype=proj.dtype, device=device)
         ops.memory_gates(raw_gates, self.gate_bias, self.gate_cap, v, top, ctx.q_start, ctx.state_slots, decay, scale,
-                         floor, v_wide, heads, self.vdim)
+                         floor, v_wide, heads, self.vdim, max_q_len=ctx.max_q_len)
         y = torch.empty((tokens, heads * self.columns), dtype=torch.float32, device=device)
         ops.linear_recurrence(
             q, k, v_wide, memory, ctx.q_start, ctx.state_slots, y, heads, heads, self.dim, self.columns,

@@ -404,7 +404,8 @@ def memory_value_columns(vdim):
     return (vdim + 1 + 3) // 4 * 4
 
 
-def memory_gates(gates, bias, cap, v, top_state, q_start, state_slots, decay, scale, floor, v_wide, heads, vdim):
+def memory_gates(gates, bias, cap, v, top_state, q_start, state_slots, decay, scale, floor, v_wide, heads, vdim,
+                 max_q_len=None):
     z = _summed(gates) + bias
     tokens = z.shape[0]
     log_in = cap * torch.tanh(z[:, :heads] / cap)

@@ -269,3 +269,40 @@ def test_normed_join_of_branches(dev, widths, kinds):
     again = torch.empty_like(out)
     ref.norm_join(terms, weights, 1e-5, again, 0.5)
     torch.testing.assert_close(again, 0.5 * want, rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("heads, kv_heads, size, page_size", [(8, 1, 64, 16), (14, 2, 64, 16), (12, 2, 128, 16),
+                                                             (4, 4, 128, 32), (40, 2, 64, 8)])
+@pytest.mark.parametrize("window", [None, 150])
+def test_tensor_core_attention_with_a_sink(dev, heads, kv_heads, size, page_size, window):
+    """The tcgen05 kernels for prompt portions and for single tokens, side by side in one step, with a
+    sink per head: one CTA per row tile, clusters that share a row tile's keys, clusters that share
+    a single token's keys and several clusters per token."""
+    from einf_b200 import ops
+    from test_kanavik_kernels import _step_split
+
+    dtype = torch.bfloat16
+    requests = [(0, 1), (0, 2 * page_size), (3, 6), (page_size * 4 - 1, 1), (700, 1), (0, 300), (2100, 64), (5000, 1)]
+    (q, k, v, table, seq, pos), scale, window = _attention_case(dev, dtype, heads, kv_heads, size, page_size, requests, window)
+    sink = (torch.randn(heads, generator=torch.Generator().manual_seed(2)) * 3).to(dev)
+    sink[0], sink[-1] = 40.0, -40.0
+    q_tiles, singles = _step_split(requests)
+    st = status(dev)
+    want = torch.empty((q.shape[0], heads, size), dtype=dtype, device=dev)
+    ref.paged_attention_generic(q, k, v, table, seq, pos, want, scale, window, st, sink=sink)
+    longest = max(s + n for s, n in requests)
+    for cluster in (0, 1, 4):
+        out = torch.full_like(want, float("nan"))
+        ops.paged_prefill_attention(q, k, v, table, q_tiles.to(dev), out, scale, window, st, prefill_cluster=cluster,
+                                    cached_before=2100, sink=sink)
+        ops.paged_decode_attention_auto(q, k, v, table, seq, pos, out, scale, window, st, singles.to(dev),
+                                        max_context=longest, sink=sink)
+        assert int(st) == 0
+        torch.testing.assert_close(out, want, **tol(dtype))
+    for cluster, splits in ((1, 1), (8, 1), (16, 1), (4, 3)):
+        out = torch.full_like(want, float("nan"))
+        ops.paged_decode_attention_tcgen05(q, k, v, table, seq, pos, out, scale, window, cluster, st, singles.to(dev),
+                                           splits, sink=sink)
+        assert int(st) == 0
+        rows = singles.long().to(dev)
+        torch.testing.assert_close(out[rows], want[rows], **tol(dtype))
