@@ -1060,6 +1060,131 @@ __global__ void qkv_norm_store_kernel(const TIn* __restrict__ qkv, int splits, s
   }
 }
 
+// The same store for rows of bfloat16 at prompt sizes: a CTA per token, a thread per 16-byte piece
+// of the row (eight elements of one head), so every load and store is a whole piece.  Sums of
+// squares meet in shared memory piece by piece, then head by head (and, for a norm over whole
+// rows, section by section), always in index order; the token's angles are made once; a rotated
+// piece finds its partner (the piece `rotary_pairs` elements on or back in the same head) in a copy
+// of the normalised row in shared memory.  No bias, no partial sums, no value mixing, halves
+// layout only, head sizes and rotated widths that are multiples of eight: the launcher sends
+// everything else to the kernel above.
+__global__ void qkv_norm_store_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ slots,
+                                             __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
+                                             __nv_bfloat16* __restrict__ v_cache, int num_heads, int num_kv_heads,
+                                             int key_size, int value_size, int normalise, float eps, int page_size,
+                                             int num_pages, const int* __restrict__ positions,
+                                             const float* __restrict__ inv_freq, int rotary_pairs,
+                                             const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                                             int values_from_keys, int* status) {
+  extern __shared__ float smem[];
+  const int qk_heads = num_heads + num_kv_heads;
+  const int qk_width = qk_heads * key_size;
+  const int width = qk_width + (values_from_keys ? 0 : num_kv_heads * value_size);
+  float* piece_squares = smem;                          // [qk_width / 8]
+  float* head_squares = piece_squares + qk_width / 8;   // [qk_heads]
+  float* cos_t = head_squares + qk_heads;               // [rotary_pairs]
+  float* sin_t = cos_t + rotary_pairs;
+  float* normed = sin_t + rotary_pairs;                 // [qk_width], only with a rotation
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int e0 = threadIdx.x * 8;
+  const bool mine = e0 < width;
+  const bool is_qk = mine && e0 < qk_width;
+  const int item = is_qk ? e0 / key_size : 0;                       // query heads, then key heads
+  const int d0 = is_qk ? e0 - item * key_size : 0;
+  const bool is_key = is_qk && item >= num_heads;
+  int page = -1, offset = 0;
+  {
+    const int slot = slots ? slots[t] : -1;
+    if (slot >= 0) {
+      page = slot / page_size;
+      offset = slot - page * page_size;
+      if (page >= num_pages) {
+        if (threadIdx.x == 0) atomicOr(status, kStatusBadPage);
+        page = -1;
+      }
+    }
+  }
+  float x[8];
+  if (mine) load8(qkv + (size_t)t * width + e0, nullptr, x);
+  if (is_key && values_from_keys && page >= 0) {
+    // the values: the keys as they came, before anything is done to them
+    const int head = item - num_heads;
+    store8(v_cache + (((size_t)page * num_kv_heads + head) * page_size + offset) * value_size + d0, x);
+  }
+  if (mine && !is_qk) {
+    if (page >= 0) {
+      const int v0 = e0 - qk_width, head = v0 / value_size;
+      store8(v_cache + (((size_t)page * num_kv_heads + head) * page_size + offset) * value_size + (v0 - head * value_size), x);
+    }
+  }
+  if (is_qk && normalise) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+    piece_squares[threadIdx.x] = ss;
+  }
+  if (rotary_pairs > 0) {
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < rotary_pairs; i += blockDim.x) sincosf(pos * inv_freq[i], &sin_t[i], &cos_t[i]);
+  }
+  __syncthreads();
+  const int pieces_per_head = key_size / 8;
+  if (normalise) {
+    if (is_qk && d0 == 0) {
+      float all = 0.f;
+      for (int i = 0; i < pieces_per_head; ++i) all += piece_squares[threadIdx.x + i];
+      head_squares[item] = all;
+    }
+    __syncthreads();
+  }
+  if (is_qk) {
+    float factor = 1.f;
+    if (normalise == 1) {
+      factor = rsqrtf(head_squares[item] / (float)key_size + eps);
+    } else if (normalise == 2) {
+      const int head0 = is_key ? num_heads : 0, count = is_key ? num_kv_heads : num_heads;
+      float all = 0.f;
+      for (int i = 0; i < count; ++i) all += head_squares[head0 + i];
+      factor = rsqrtf(all / (float)(count * key_size) + eps);
+    }
+    const float* weight = is_key ? k_weight : q_weight;
+    if (weight) {
+      const float* w = weight + (normalise == 2 ? (is_key ? (item - num_heads) * key_size : item * key_size) : 0) + d0;
+      const float4 w0 = *reinterpret_cast<const float4*>(w), w1 = *reinterpret_cast<const float4*>(w + 4);
+      const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] *= factor * ws[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] *= factor;
+    }
+    if (rotary_pairs > 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) normed[e0 + i] = x[i];
+    }
+  }
+  if (rotary_pairs > 0) {
+    __syncthreads();
+    if (is_qk && d0 < 2 * rotary_pairs) {
+      const bool leads = d0 < rotary_pairs;
+      const int pair0 = leads ? d0 : d0 - rotary_pairs;
+      const float* other = normed + (leads ? e0 + rotary_pairs : e0 - rotary_pairs);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float cs = cos_t[pair0 + i], sn = sin_t[pair0 + i];
+        x[i] = leads ? x[i] * cs - other[i] * sn : x[i] * cs + other[i] * sn;
+      }
+    }
+  }
+  if (is_qk && !is_key) store8(q_out + ((size_t)t * num_heads + item) * key_size + d0, x);
+  if (is_key && page >= 0) {
+    const int head = item - num_heads;
+    store8(k_cache + (((size_t)page * num_kv_heads + head) * page_size + offset) * key_size + d0, x);
+  }
+}
+
 // out[m, n] += bias[n]: the bias of a matrix product that a library computed.
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ out, const float* __restrict__ bias, int n, size_t total) {
@@ -1463,6 +1588,25 @@ extern "C" int einf_qkv_norm_store(const void* qkv, int in_dtype, int splits, lo
   if (value_mix && (!shared_values || (value_mix == 2 && !mix))) return (int)cudaErrorInvalidValue;
   if (key_size > 256 || value_size > 256 || key_size <= 0 || (num_kv_heads > 0 && value_size <= 0))
     return (int)cudaErrorInvalidValue;
+  // rows of bfloat16 at prompt sizes: whole 16-byte pieces, a CTA per token
+  {
+    const int qk_width = (num_heads + num_kv_heads) * key_size;
+    const int width = qk_width + (values_from_keys ? 0 : num_kv_heads * value_size);
+    const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache |
+                           (uintptr_t)q_weight | (uintptr_t)k_weight) & 15) == 0;
+    if (in_dtype == kBFloat16 && dtype == kBFloat16 && splits <= 1 && !bias && !value_mix && !interleaved &&
+        num_tokens >= 64 && key_size % 8 == 0 && value_size % 8 == 0 && rotary_pairs % 8 == 0 && width <= 8192 &&
+        num_kv_heads > 0 && aligned) {
+      const int threads = (width / 8 + 31) / 32 * 32;
+      const size_t bytes = (size_t)(qk_width / 8 + num_heads + num_kv_heads + 2 * rotary_pairs +
+                                    (rotary_pairs > 0 ? qk_width : 0)) * sizeof(float);
+      return (int)launch_pdl(qkv_norm_store_bf16x8_kernel, num_tokens, threads, bytes, stream,
+                             (const __nv_bfloat16*)qkv, slots, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
+                             (__nv_bfloat16*)v_cache, num_heads, num_kv_heads, key_size, value_size, normalise, eps,
+                             page_size, num_pages, positions, inv_freq, rotary_pairs, q_weight, k_weight,
+                             values_from_keys, status);
+    }
+  }
   const long long warps = (long long)num_tokens * (num_heads + 2 * num_kv_heads);
   const int threads = token_blocks ? 32 * (num_heads + 2 * num_kv_heads) : 128;
   const long long blocks = token_blocks ? num_tokens : (warps * 32 + threads - 1) / threads;

@@ -410,8 +410,9 @@ __global__ void recurrence_walk_kernel(const __grid_constant__ RecurrenceArgs a)
 
 // One token per request (a decode step): the state is streamed through once, four columns a
 // thread with 16-byte loads and stores along the rows, S <- a S + k (s v)^T and the thread's part of
-// y = S^T q in the same pass; the row groups' parts of y meet in shared memory.  vdim / 4 must
-// divide the 128 threads (the launcher sends other sizes to the kernel above).
+// y = S^T q in the same pass; the row groups' parts of y meet in shared memory.  vdim / 4 is at most
+// the 128 threads (the launcher sends other sizes to the kernel above); where it does not divide
+// them, the threads beyond the last whole row group sit the pass out.
 template <typename T>
 __global__ void __launch_bounds__(kRecurrenceThreads)
 recurrence_step_kernel(const __grid_constant__ RecurrenceArgs a) {
@@ -444,14 +445,15 @@ recurrence_step_kernel(const __grid_constant__ RecurrenceArgs a) {
     vs[i] = scale * (act ? silu_f(v) : v);
   }
   __syncthreads();
-  const int quads = vdim >> 2;                       // divides 128
+  const int quads = vdim >> 2;                       // at most 128
   const int cq = threadIdx.x % quads, row0 = threadIdx.x / quads, row_step = kRecurrenceThreads / quads;
+  const bool works = row0 < row_step;                // false: a thread beyond the last whole row group
   const float4 sv = *reinterpret_cast<const float4*>(vs + 4 * cq);
   float4* state = (slot >= 0 && slot < a.num_slots)
       ? reinterpret_cast<float4*>(a.state + (long long)slot * a.state_stride + ((long long)head * dim) * vdim) + cq : nullptr;
   float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
   constexpr int kInFlight = 8;
-  for (int row = row0; row < dim; row += row_step * kInFlight) {
+  for (int row = works ? row0 : dim; row < dim; row += row_step * kInFlight) {
     float4 s[kInFlight];
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {
@@ -474,7 +476,7 @@ recurrence_step_kernel(const __grid_constant__ RecurrenceArgs a) {
       if (state) state[(long long)rr * quads] = s[u];
     }
   }
-  *reinterpret_cast<float4*>(parts + row0 * vdim + 4 * cq) = y;
+  if (works) *reinterpret_cast<float4*>(parts + row0 * vdim + 4 * cq) = y;
   __syncthreads();
   const float skip = a.skip ? a.skip[head] : 0.f;
   for (int c = threadIdx.x; c < vdim; c += kRecurrenceThreads) {
@@ -532,10 +534,10 @@ __global__ void gated_norm_kernel(const float* __restrict__ y, const T* __restri
 // sums), m the running maximum that lives in top_state[slot * top_stride + head] (zero after a
 // fresh start; a request without a slot starts from zero and stores nothing).  decay and scale are
 // what the linear recurrence multiplies its state and its input by; they never exceed one.
-// The CTAs (x, request) of a request each widen the values of a share of its tokens for the
+// The CTAs (x > 0, request) of a request each widen the values of a share of its tokens for the
 // recurrence, v_wide[t, h] = [v[t, h] | 1 | 0 ...] of `columns` elements, so that the memory's
 // normaliser (the same recurrence on the keys alone) is one more column of its state.  CTA 0 of
-// the request also makes the gates: the capped logarithms of all its tokens side by side (left in
+// the request makes the gates: the capped logarithms of all its tokens side by side (left in
 // `scale` and `decay`), then a warp per head walks the maxima.  A step m -> max(m + f, i) is a pair
 // (f, i), and two steps in a row are the pair (f1 + f2, max(i1 + f2, i2)): every lane folds a run
 // of tokens into one pair, a scan over the warp's 32 pairs gives every lane the maximum its run
@@ -559,20 +561,22 @@ memory_gates_kernel(const float* __restrict__ gates, int splits, size_t split_st
   const int first = q_start[r], last = q_start[r + 1];
   const int count = last - first;
   if (count <= 0) return;
-  {
-    // this CTA's share of the request's tokens, widened
-    const int per = (count + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int t0 = first + (int)blockIdx.x * per, t1 = min(last, t0 + per);
-    const int wide = heads * columns;
-    for (long long i = threadIdx.x; i < (long long)max(0, t1 - t0) * wide; i += blockDim.x) {
-      const int t = t0 + (int)(i / wide), c = (int)(i % wide);
-      const int h = c / columns, d = c - h * columns;
-      T value = from_float<T>(d == vdim ? 1.f : 0.f);
-      if (d < vdim) value = v[(long long)t * v_stride + h * vdim + d];
-      v_wide[(size_t)t * wide + c] = value;
+  if (blockIdx.x > 0) {
+    // this CTA's share of the request's tokens, widened: a warp per (token, head) row
+    const int shares = (int)gridDim.x - 1;
+    const int per = (count + shares - 1) / shares;
+    const int t0 = first + ((int)blockIdx.x - 1) * per, t1 = min(last, t0 + per);
+    const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int rows = max(0, t1 - t0) * heads;
+    for (int row = threadIdx.x >> 5; row < rows; row += warps) {
+      const int t = t0 + row / heads, h = row % heads;
+      const T* src = v + (long long)t * v_stride + h * vdim;
+      T* dst = v_wide + ((size_t)t * heads + h) * columns;
+      for (int d = lane; d < columns; d += 32)
+        dst[d] = d < vdim ? src[d] : from_float<T>(d == vdim ? 1.f : 0.f);
     }
+    return;
   }
-  if (blockIdx.x != 0) return;
   const int slot = state_slots[r];
   const bool kept = slot >= 0 && slot < num_slots;
   const float inv_cap = 1.f / cap;
@@ -881,7 +885,7 @@ extern "C" int einf_linear_recurrence(const void* q, const void* k, const void* 
   a.num_slots = num_slots; a.heads = heads; a.groups = groups; a.dim = dim; a.vdim = vdim; a.act = act;
   a.segments = segments; a.segment_len = segment_len;
   // A step of single tokens (segment_len 1 says so): the streaming kernel, where it takes the sizes.
-  if (segments == 1 && segment_len == 1 && vdim % 4 == 0 && kRecurrenceThreads % (vdim / 4) == 0 &&
+  if (segments == 1 && segment_len == 1 && vdim % 4 == 0 && vdim / 4 <= kRecurrenceThreads &&
       state_stride % 4 == 0 && ((uintptr_t)state & 15) == 0) {
     a.lanes_per_column = 0; a.dim_pad = dim; a.batch = 1;
     const int row_groups = kRecurrenceThreads / (vdim / 4);
@@ -990,7 +994,7 @@ extern "C" int einf_memory_gates(const float* gates, int splits, long long split
   if (longest <= 0) longest = num_tokens;
   int shares = (longest + 15) / 16;
   shares = shares < 1 ? 1 : (shares > 128 ? 128 : shares);
-  const dim3 grid(shares, num_requests);
+  const dim3 grid(shares + 1, num_requests);      // CTA 0 of a request makes its gates, the others widen its values
   EINF_DISPATCH_2(dtype, T, {
     return (int)launch_pdl(memory_gates_kernel<T>, grid, dim3(256), 0, stream, gates, splits < 1 ? 1 : splits,
                            (size_t)split_stride, bias, cap, (const T*)v, v_stride, top_state, top_stride, num_slots,

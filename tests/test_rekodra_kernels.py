@@ -42,15 +42,19 @@ def test_embedding_and_logits_take_a_factor(dev):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, kv_heads, size, pairs, norm", [
     (4, 2, 16, 4, "head"), (3, 1, 24, 12, "row"), (8, 1, 64, 16, "row"), (6, 6, 64, 0, "head"), (5, 5, 40, 20, "row"),
-    (2, 2, 256, 0, "row"), (1, 1, 8, 4, "head"),
+    (2, 2, 256, 0, "row"), (1, 1, 8, 4, "head"), (24, 8, 16, 8, "row"), (12, 2, 128, 32, "row"), (14, 2, 64, 32, "head"),
 ])
 @pytest.mark.parametrize("values", ["keys", "projected"])
 @pytest.mark.parametrize("splits", [1, 3])
-def test_store_with_weighted_norms_and_values_from_keys(dev, dtype, heads, kv_heads, size, pairs, norm, values, splits):
+@pytest.mark.parametrize("tokens", [23, 150])
+def test_store_with_weighted_norms_and_values_from_keys(dev, dtype, heads, kv_heads, size, pairs, norm, values, splits,
+                                                        tokens):
+    """A few rows and partial sums take the kernel of a warp per head; 150 rows of bfloat16 whose sizes
+    are multiples of eight take the kernel of 16-byte pieces."""
     from einf_b200 import ops
 
     gen = torch.Generator().manual_seed(3)
-    tokens, page_size, pages, value_size = 23, 4, 9, size if values == "keys" else 24
+    page_size, pages, value_size = 4, tokens // 4 + 4, size if values == "keys" else 24
     width = (heads + kv_heads) * size + (0 if values == "keys" else kv_heads * value_size)
     if splits == 1:
         qkv = torch.randn((tokens, width), generator=gen).to(dtype).to(dev)
