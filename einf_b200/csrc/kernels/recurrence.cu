@@ -537,16 +537,14 @@ __global__ void gated_norm_kernel(const float* __restrict__ y, const T* __restri
 // The CTAs (x > 0, request) of a request each widen the values of a share of its tokens for the
 // recurrence, v_wide[t, h] = [v[t, h] | 1 | 0 ...] of `columns` elements, so that the memory's
 // normaliser (the same recurrence on the keys alone) is one more column of its state.  CTA 0 of
-// the request makes the gates: the capped logarithms of all its tokens side by side (left in
-// `scale` and `decay`), then a warp per head walks the maxima.  A step m -> max(m + f, i) is a pair
-// (f, i), and two steps in a row are the pair (f1 + f2, max(i1 + f2, i2)): every lane folds a run
-// of tokens into one pair, a scan over the warp's 32 pairs gives every lane the maximum its run
-// starts from, and the lane walks its run again, now with the exponentials.  The maximum only
-// sets the scale that state, normaliser and floor share, so the order of these sums moves no result
-// beyond the rounding of that scale.
+// the request makes the gates, a warp per head: a step m -> max(m + f, i) is a pair (f, i), and two
+// steps in a row are the pair (f1 + f2, max(i1 + f2, i2)); the warp takes 32 tokens at a time, a
+// lane each, a scan over the lanes' pairs gives every lane its token's maximum from the one the
+// tile starts with, and the last lane's is the next tile's start.  Nothing passes through memory
+// on the way.  The maximum only sets the scale that state, normaliser and floor share, so the
+// order of these sums moves no result beyond the rounding of that scale.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
-constexpr int kGateBatch = 8;      // tokens whose logarithms a lane fetches before it walks them
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -581,91 +579,57 @@ memory_gates_kernel(const float* __restrict__ gates, int splits, size_t split_st
   const bool kept = slot >= 0 && slot < num_slots;
   const float inv_cap = 1.f / cap;
   const int width = 2 * heads;
-  if (count == 1) {
-    // a single token (decoding): a thread per head, nothing passes through memory on the way
-    for (int h = threadIdx.x; h < heads; h += blockDim.x) {
-      float zi = bias[h], zf = bias[heads + h];
-      for (int s = 0; s < splits; ++s) {
-        zi += gates[(size_t)s * split_stride + (size_t)first * width + h];
-        zf += gates[(size_t)s * split_stride + (size_t)first * width + heads + h];
-      }
-      const float log_in = cap * tanhf(zi * inv_cap), log_keep = log_sigmoid_f(cap * tanhf(zf * inv_cap));
-      const float m = kept ? top_state[(long long)slot * top_stride + h] : 0.f;
-      const float m_new = fmaxf(log_keep + m, log_in);
-      const size_t at = (size_t)first * heads + h;
-      decay[at] = expf(log_keep + m - m_new);
-      scale[at] = expf(log_in - m_new);
-      floor[at] = expf(-m_new);
-      if (kept) top_state[(long long)slot * top_stride + h] = m_new;
-    }
-    return;
-  }
-  for (int i = threadIdx.x; i < count * heads; i += blockDim.x) {
-    const int t = first + i / heads, h = i % heads;
-    float zi = bias[h], zf = bias[heads + h];
-    for (int s = 0; s < splits; ++s) {
-      zi += gates[(size_t)s * split_stride + (size_t)t * width + h];
-      zf += gates[(size_t)s * split_stride + (size_t)t * width + heads + h];
-    }
-    scale[(size_t)t * heads + h] = cap * tanhf(zi * inv_cap);
-    decay[(size_t)t * heads + h] = log_sigmoid_f(cap * tanhf(zf * inv_cap));
-  }
-  __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int run = (count + 31) / 32;
-  const int run_first = min(last, first + lane * run), run_last = min(last, run_first + run);
   for (int h = warp; h < heads; h += (int)(blockDim.x >> 5)) {
-    // this lane's run of tokens as one step (kGateBatch tokens' loads in flight at a time)
-    float add = 0.f, least = -INFINITY;
-    for (int t0 = run_first; t0 < run_last; t0 += kGateBatch) {
-      float log_keep[kGateBatch], log_in[kGateBatch];
-#pragma unroll
-      for (int u = 0; u < kGateBatch; ++u) {
-        const bool in = t0 + u < run_last;
-        log_keep[u] = in ? decay[(size_t)(t0 + u) * heads + h] : 0.f;
-        log_in[u] = in ? scale[(size_t)(t0 + u) * heads + h] : -INFINITY;
+    float carry = kept ? top_state[(long long)slot * top_stride + h] : 0.f;      // the maximum before the tile
+    const float bias_in = bias[h], bias_keep = bias[heads + h];
+    // a tile's raw gates are fetched while the tile before it is scanned
+    auto fetch = [&](int t, float& zi, float& zf) {
+      zi = bias_in;
+      zf = bias_keep;
+      if (t >= last) return;
+      for (int s = 0; s < splits; ++s) {
+        zi += gates[(size_t)s * split_stride + (size_t)t * width + h];
+        zf += gates[(size_t)s * split_stride + (size_t)t * width + heads + h];
       }
-#pragma unroll
-      for (int u = 0; u < kGateBatch; ++u) {      // a token beyond the run is the step that changes nothing
-        add += log_keep[u];
-        least = fmaxf(least + log_keep[u], log_in[u]);
+    };
+    float zi_next, zf_next;
+    fetch(first + lane, zi_next, zf_next);
+    for (int t0 = first; t0 < last; t0 += 32) {
+      const int t = t0 + lane;
+      const bool in = t < last;
+      const float zi = zi_next, zf = zf_next;
+      fetch(t + 32, zi_next, zf_next);
+      // a token beyond the request is the step that changes nothing: (0, -inf)
+      float add = 0.f, least = -INFINITY;
+      if (in) {
+        least = cap * tanhf(zi * inv_cap);
+        add = log_sigmoid_f(cap * tanhf(zf * inv_cap));
       }
+      const float log_in = least, log_keep = add;
+      // the steps of the tile's tokens 0 .. lane in a row
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float add_before = __shfl_up_sync(0xffffffffu, add, o);
+        const float least_before = __shfl_up_sync(0xffffffffu, least, o);
+        if (lane >= o) {
+          least = fmaxf(least_before + add, least);
+          add += add_before;
+        }
+      }
+      const float m = fmaxf(carry + add, least);                 // the maximum behind this token
+      float before = __shfl_up_sync(0xffffffffu, m, 1);
+      if (lane == 0) before = carry;
+      if (in) {
+        const size_t at = (size_t)t * heads + h;
+        // neither exponent is positive; the scan's sums may leave one a rounding above zero
+        decay[at] = expf(fminf(log_keep + before - m, 0.f));
+        scale[at] = expf(fminf(log_in - m, 0.f));
+        floor[at] = expf(-m);
+      }
+      carry = __shfl_sync(0xffffffffu, m, 31);
     }
-    // the steps of lanes 0 .. lane in a row
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float add_before = __shfl_up_sync(0xffffffffu, add, o);
-      const float least_before = __shfl_up_sync(0xffffffffu, least, o);
-      if (lane >= o) {
-        least = fmaxf(least_before + add, least);
-        add += add_before;
-      }
-    }
-    const float start = kept ? top_state[(long long)slot * top_stride + h] : 0.f;
-    const float after = fmaxf(start + add, least);           // the maximum behind this lane's run
-    float m = __shfl_up_sync(0xffffffffu, after, 1);
-    if (lane == 0) m = start;
-    for (int t0 = run_first; t0 < run_last; t0 += kGateBatch) {
-      float log_keep[kGateBatch], log_in[kGateBatch];
-#pragma unroll
-      for (int u = 0; u < kGateBatch; ++u) {
-        const bool in = t0 + u < run_last;
-        log_keep[u] = in ? decay[(size_t)(t0 + u) * heads + h] : 0.f;
-        log_in[u] = in ? scale[(size_t)(t0 + u) * heads + h] : -INFINITY;
-      }
-#pragma unroll
-      for (int u = 0; u < kGateBatch; ++u) {
-        if (t0 + u >= run_last) break;
-        const size_t at = (size_t)(t0 + u) * heads + h;
-        const float m_new = fmaxf(log_keep[u] + m, log_in[u]);
-        decay[at] = expf(log_keep[u] + m - m_new);
-        scale[at] = expf(log_in[u] - m_new);
-        floor[at] = expf(-m_new);
-        m = m_new;
-      }
-    }
-    const float end = __shfl_sync(0xffffffffu, after, 31);
-    if (lane == 0 && kept) top_state[(long long)slot * top_stride + h] = end;
+    if (lane == 0 && kept) top_state[(long long)slot * top_stride + h] = carry;
   }
 }
 
