@@ -1212,7 +1212,7 @@ __device__ __forceinline__ float join_value(const JoinTerm& term, size_t at) {
   return to_float(((const __nv_bfloat16*)term.x)[at]);
 }
 
-constexpr int kJoinKeep = 8;
+constexpr int kJoinKeep = 16;
 
 __global__ void norm_join_kernel(const __grid_constant__ JoinArgs a, float eps, float scale, float* __restrict__ out,
                                  int width) {
@@ -1660,5 +1660,12 @@ extern "C" int einf_norm_join(int terms,
   for (int i = 0; i < terms; ++i)
     if (!a.term[i].x || !a.term[i].weight || (a.term[i].dtype != kFloat32 && a.term[i].splits > 1))
       return (int)cudaErrorInvalidValue;
-  return (int)launch_pdl(norm_join_kernel, rows, pick_threads(width), 0, stream, a, eps, scale, out, width);
+  // many rows: few warps a row, sixteen elements a thread (fewer barriers, more CTAs an SM); a few rows: more
+  // threads a row, so that each has less to wait for
+  int threads = pick_threads(width);
+  if (rows >= 256) {
+    threads = ((width + kJoinKeep - 1) / kJoinKeep + 31) / 32 * 32;
+    threads = threads < 32 ? 32 : (threads > 256 ? 256 : threads);
+  }
+  return (int)launch_pdl(norm_join_kernel, rows, threads, 0, stream, a, eps, scale, out, width);
 }

@@ -250,11 +250,12 @@ def test_matrix_memory_steps(dev, dtype, heads, dim, vdim, cap, portions):
 
 @pytest.mark.parametrize("widths", [(48,), (200,), (1536,), (5000,)])
 @pytest.mark.parametrize("kinds", [("f32", "bf16"), ("split", "f32"), ("bf16",), ("split", "split", "f32", "bf16")])
-def test_normed_join_of_branches(dev, widths, kinds):
+@pytest.mark.parametrize("tokens", [19, 300])
+def test_normed_join_of_branches(dev, widths, kinds, tokens):
     from einf_b200 import ops
 
     gen = torch.Generator().manual_seed(17)
-    tokens, width = 19, widths[0]
+    width = widths[0]
     terms, weights = [], []
     for index, kind in enumerate(kinds):
         if kind == "split":
