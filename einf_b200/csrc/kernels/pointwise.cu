@@ -1212,7 +1212,7 @@ __device__ __forceinline__ float join_value(const JoinTerm& term, size_t at) {
   return to_float(((const __nv_bfloat16*)term.x)[at]);
 }
 
-constexpr int kJoinKeep = 16;
+constexpr int kJoinKeep = 8;
 
 __global__ void norm_join_kernel(const __grid_constant__ JoinArgs a, float eps, float scale, float* __restrict__ out,
                                  int width) {
@@ -1260,6 +1260,75 @@ __global__ void norm_join_kernel(const __grid_constant__ JoinArgs a, float eps, 
     float v = 0.f;
     for (int i = 0; i < a.terms; ++i) v += a.term[i].weight[d] * (join_value(a.term[i], row + d) * factor[i]);
     out[row + d] = scale * v;
+  }
+}
+
+// The same for many rows whose width is a multiple of eight and one or two terms: a warp per row,
+// a lane holds kChunks pieces of eight elements of either term (16-byte loads of bfloat16, two of
+// floats), all of them asked for before the first sum of squares, and the row stays in registers up
+// to the output.
+template <int kChunks>
+__device__ __forceinline__ void join_load_row(const JoinTerm& term, size_t base, int lane, int width, float (&x)[kChunks][8]) {
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int d = (c * 32 + lane) * 8;
+    if (d < width) {
+      if (term.dtype == kFloat32) {
+        const float4 lo = load4((const float*)term.x + base + d), hi = load4((const float*)term.x + base + d + 4);
+        x[c][0] = lo.x; x[c][1] = lo.y; x[c][2] = lo.z; x[c][3] = lo.w;
+        x[c][4] = hi.x; x[c][5] = hi.y; x[c][6] = hi.z; x[c][7] = hi.w;
+      } else {
+        load8((const __nv_bfloat16*)term.x + base + d, nullptr, x[c]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[c][i] = 0.f;
+    }
+  }
+}
+
+template <int kChunks>
+__global__ void norm_join_warp_kernel(const __grid_constant__ JoinArgs a, float eps, float scale,
+                                      float* __restrict__ out, int rows, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const size_t base = (size_t)row * width;
+  const bool two = a.terms > 1;
+  float x0[kChunks][8], x1[kChunks][8];
+  join_load_row<kChunks>(a.term[0], base, lane, width, x0);
+  if (two) join_load_row<kChunks>(a.term[1], base, lane, width, x1);
+  float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      ss0 += x0[c][i] * x0[c][i];
+      if (two) ss1 += x1[c][i] * x1[c][i];
+    }
+  const float f0 = rsqrtf(warp_sum(ss0) / (float)width + eps);
+  const float f1 = two ? rsqrtf(warp_sum(ss1) / (float)width + eps) : 0.f;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int d = (c * 32 + lane) * 8;
+    if (d >= width) continue;
+    float v[8];
+    {
+      const float4 w0 = load4(a.term[0].weight + d), w1 = load4(a.term[0].weight + d + 4);
+      const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = w[i] * (x0[c][i] * f0);
+    }
+    if (two) {
+      const float4 w0 = load4(a.term[1].weight + d), w1 = load4(a.term[1].weight + d + 4);
+      const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += w[i] * (x1[c][i] * f1);
+    }
+    store4(out + base + d, make_float4(scale * v[0], scale * v[1], scale * v[2], scale * v[3]));
+    store4(out + base + d + 4, make_float4(scale * v[4], scale * v[5], scale * v[6], scale * v[7]));
   }
 }
 
@@ -1660,12 +1729,20 @@ extern "C" int einf_norm_join(int terms,
   for (int i = 0; i < terms; ++i)
     if (!a.term[i].x || !a.term[i].weight || (a.term[i].dtype != kFloat32 && a.term[i].splits > 1))
       return (int)cudaErrorInvalidValue;
-  // many rows: few warps a row, sixteen elements a thread (fewer barriers, more CTAs an SM); a few rows: more
-  // threads a row, so that each has less to wait for
-  int threads = pick_threads(width);
-  if (rows >= 256) {
-    threads = ((width + kJoinKeep - 1) / kJoinKeep + 31) / 32 * 32;
-    threads = threads < 32 ? 32 : (threads > 256 ? 256 : threads);
+  // many rows of whole 16-byte pieces, one or two terms: a warp per row, the row in registers
+  bool pieces = rows >= 64 && terms <= 2 && width % 8 == 0 && width <= 32 * 8 * 8 && ((uintptr_t)out & 15) == 0;
+  for (int i = 0; i < terms; ++i)
+    pieces = pieces && a.term[i].splits <= 1 && ((uintptr_t)a.term[i].x & 15) == 0 && ((uintptr_t)a.term[i].weight & 15) == 0;
+  if (pieces) {
+    const int warps = 4;
+    const int blocks = (rows + warps - 1) / warps;
+    if (width <= 32 * 8 * 2)
+      return (int)launch_pdl(norm_join_warp_kernel<2>, blocks, warps * 32, 0, stream, a, eps, scale, out, rows, width);
+    if (width <= 32 * 8 * 4)
+      return (int)launch_pdl(norm_join_warp_kernel<4>, blocks, warps * 32, 0, stream, a, eps, scale, out, rows, width);
+    if (width <= 32 * 8 * 6)
+      return (int)launch_pdl(norm_join_warp_kernel<6>, blocks, warps * 32, 0, stream, a, eps, scale, out, rows, width);
+    return (int)launch_pdl(norm_join_warp_kernel<8>, blocks, warps * 32, 0, stream, a, eps, scale, out, rows, width);
   }
-  return (int)launch_pdl(norm_join_kernel, rows, threads, 0, stream, a, eps, scale, out, width);
+  return (int)launch_pdl(norm_join_kernel, rows, pick_threads(width), 0, stream, a, eps, scale, out, width);
 }
