@@ -534,17 +534,20 @@ __global__ void gated_norm_kernel(const float* __restrict__ y, const T* __restri
 // sums), m the running maximum that lives in top_state[slot * top_stride + head] (zero after a
 // fresh start; a request without a slot starts from zero and stores nothing).  decay and scale are
 // what the linear recurrence multiplies its state and its input by; they never exceed one.
-// The CTAs (x > 0, request) of a request each widen the values of a share of its tokens for the
-// recurrence, v_wide[t, h] = [v[t, h] | 1 | 0 ...] of `columns` elements, so that the memory's
-// normaliser (the same recurrence on the keys alone) is one more column of its state.  CTA 0 of
-// the request makes the gates, a warp per head: a step m -> max(m + f, i) is a pair (f, i), and two
-// steps in a row are the pair (f1 + f2, max(i1 + f2, i2)); the warp takes 32 tokens at a time, a
+// The CTAs (x >= heads, request) of a request each widen the values of a share of its tokens for
+// the recurrence, v_wide[t, h] = [v[t, h] | 1 | 0 ...] of `columns` elements, so that the memory's
+// normaliser (the same recurrence on the keys alone) is one more column of its state.  CTA h < heads
+// of the request makes the gates of head h: a step m -> max(m + f, i) is a pair (f, i), and two
+// steps in a row are the pair (f1 + f2, max(i1 + f2, i2)); a warp takes 32 tokens at a time, a
 // lane each, a scan over the lanes' pairs gives every lane its token's maximum from the one the
-// tile starts with, and the last lane's is the next tile's start.  Nothing passes through memory
-// on the way.  The maximum only sets the scale that state, normaliser and floor share, so the
+// tile starts with, and the last lane's is the next tile's start.  A portion of more than 256 tokens
+// is cut into a range per warp: every warp first folds its range into one pair, the pairs of the
+// ranges before it give the maximum its range starts from, and it walks the range again.  Nothing
+// passes through memory on the way.  The maximum only sets the scale that state, normaliser and floor share, so the
 // order of these sums moves no result beyond the rounding of that scale.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+constexpr int kGateWarps = 8;      // warps of a CTA of the gate kernel
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -559,11 +562,11 @@ memory_gates_kernel(const float* __restrict__ gates, int splits, size_t split_st
   const int first = q_start[r], last = q_start[r + 1];
   const int count = last - first;
   if (count <= 0) return;
-  if (blockIdx.x > 0) {
+  if ((int)blockIdx.x >= heads) {
     // this CTA's share of the request's tokens, widened: a warp per (token, head) row
-    const int shares = (int)gridDim.x - 1;
+    const int shares = (int)gridDim.x - heads;
     const int per = (count + shares - 1) / shares;
-    const int t0 = first + ((int)blockIdx.x - 1) * per, t1 = min(last, t0 + per);
+    const int t0 = first + ((int)blockIdx.x - heads) * per, t1 = min(last, t0 + per);
     const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int rows = max(0, t1 - t0) * heads;
     for (int row = threadIdx.x >> 5; row < rows; row += warps) {
@@ -575,62 +578,100 @@ memory_gates_kernel(const float* __restrict__ gates, int splits, size_t split_st
     }
     return;
   }
+  __shared__ float range_add[kGateWarps], range_least[kGateWarps];
+  const int h = blockIdx.x;
   const int slot = state_slots[r];
   const bool kept = slot >= 0 && slot < num_slots;
   const float inv_cap = 1.f / cap;
   const int width = 2 * heads;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int h = warp; h < heads; h += (int)(blockDim.x >> 5)) {
-    float carry = kept ? top_state[(long long)slot * top_stride + h] : 0.f;      // the maximum before the tile
-    const float bias_in = bias[h], bias_keep = bias[heads + h];
-    // a tile's raw gates are fetched while the tile before it is scanned
-    auto fetch = [&](int t, float& zi, float& zf) {
-      zi = bias_in;
-      zf = bias_keep;
-      if (t >= last) return;
-      for (int s = 0; s < splits; ++s) {
-        zi += gates[(size_t)s * split_stride + (size_t)t * width + h];
-        zf += gates[(size_t)s * split_stride + (size_t)t * width + heads + h];
-      }
-    };
-    float zi_next, zf_next;
-    fetch(first + lane, zi_next, zf_next);
-    for (int t0 = first; t0 < last; t0 += 32) {
-      const int t = t0 + lane;
-      const bool in = t < last;
-      const float zi = zi_next, zf = zf_next;
-      fetch(t + 32, zi_next, zf_next);
-      // a token beyond the request is the step that changes nothing: (0, -inf)
-      float add = 0.f, least = -INFINITY;
-      if (in) {
-        least = cap * tanhf(zi * inv_cap);
-        add = log_sigmoid_f(cap * tanhf(zf * inv_cap));
-      }
-      const float log_in = least, log_keep = add;
-      // the steps of the tile's tokens 0 .. lane in a row
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float add_before = __shfl_up_sync(0xffffffffu, add, o);
-        const float least_before = __shfl_up_sync(0xffffffffu, least, o);
-        if (lane >= o) {
-          least = fmaxf(least_before + add, least);
-          add += add_before;
-        }
-      }
-      const float m = fmaxf(carry + add, least);                 // the maximum behind this token
-      float before = __shfl_up_sync(0xffffffffu, m, 1);
-      if (lane == 0) before = carry;
-      if (in) {
-        const size_t at = (size_t)t * heads + h;
-        // neither exponent is positive; the scan's sums may leave one a rounding above zero
-        decay[at] = expf(fminf(log_keep + before - m, 0.f));
-        scale[at] = expf(fminf(log_in - m, 0.f));
-        floor[at] = expf(-m);
-      }
-      carry = __shfl_sync(0xffffffffu, m, 31);
+  const float bias_in = bias[h], bias_keep = bias[heads + h];
+  // a tile's raw gates are fetched while the tile before it is scanned
+  auto fetch = [&](int t, int t_end, float& zi, float& zf) {
+    zi = bias_in;
+    zf = bias_keep;
+    if (t >= t_end) return;
+    for (int s = 0; s < splits; ++s) {
+      zi += gates[(size_t)s * split_stride + (size_t)t * width + h];
+      zf += gates[(size_t)s * split_stride + (size_t)t * width + heads + h];
     }
-    if (lane == 0 && kept) top_state[(long long)slot * top_stride + h] = carry;
+  };
+  // One tile: the capped logarithms of the lane's token, and the steps of the tile's tokens 0 .. lane in a row.
+  // A token beyond the range is the step that changes nothing: (0, -inf).
+  auto scan_tile = [&](bool in, float zi, float zf, float& log_in, float& log_keep, float& add, float& least) {
+    add = 0.f;
+    least = -INFINITY;
+    if (in) {
+      least = cap * tanhf(zi * inv_cap);
+      add = log_sigmoid_f(cap * tanhf(zf * inv_cap));
+    }
+    log_in = least;
+    log_keep = add;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float add_before = __shfl_up_sync(0xffffffffu, add, o);
+      const float least_before = __shfl_up_sync(0xffffffffu, least, o);
+      if (lane >= o) {
+        least = fmaxf(least_before + add, least);
+        add += add_before;
+      }
+    }
+  };
+  // A short portion is one warp's; a long one is cut into a range of whole tiles per warp, and every
+  // warp first folds its range into one step so that each knows the maximum its range starts from.
+  const bool ranges = count > 8 * 32;
+  if (!ranges && warp > 0) return;
+  int range_first = first, range_last = last;
+  if (ranges) {
+    const int per = ((count + kGateWarps - 1) / kGateWarps + 31) / 32 * 32;
+    range_first = min(last, first + warp * per);
+    range_last = min(last, range_first + per);
   }
+  float carry = kept ? top_state[(long long)slot * top_stride + h] : 0.f;      // the maximum before the tile
+  if (ranges) {
+    float run_add = 0.f, run_least = -INFINITY;
+    float zi_next, zf_next;
+    fetch(range_first + lane, range_last, zi_next, zf_next);
+    for (int t0 = range_first; t0 < range_last; t0 += 32) {
+      const float zi = zi_next, zf = zf_next;
+      fetch(t0 + lane + 32, range_last, zi_next, zf_next);
+      float log_in, log_keep, add, least;
+      scan_tile(t0 + lane < range_last, zi, zf, log_in, log_keep, add, least);
+      const float tile_add = __shfl_sync(0xffffffffu, add, 31), tile_least = __shfl_sync(0xffffffffu, least, 31);
+      run_least = fmaxf(run_least + tile_add, tile_least);
+      run_add += tile_add;
+    }
+    if (lane == 0) {
+      range_add[warp] = run_add;
+      range_least[warp] = run_least;
+    }
+    __syncthreads();
+    for (int w = 0; w < warp; ++w) carry = fmaxf(carry + range_add[w], range_least[w]);
+  }
+  float zi_next, zf_next;
+  fetch(range_first + lane, range_last, zi_next, zf_next);
+  for (int t0 = range_first; t0 < range_last; t0 += 32) {
+    const int t = t0 + lane;
+    const bool in = t < range_last;
+    const float zi = zi_next, zf = zf_next;
+    fetch(t + 32, range_last, zi_next, zf_next);
+    float log_in, log_keep, add, least;
+    scan_tile(in, zi, zf, log_in, log_keep, add, least);
+    const float m = fmaxf(carry + add, least);                 // the maximum behind this token
+    float before = __shfl_up_sync(0xffffffffu, m, 1);
+    if (lane == 0) before = carry;
+    if (in) {
+      const size_t at = (size_t)t * heads + h;
+      // neither exponent is positive; the scan's sums may leave one a rounding above zero
+      decay[at] = expf(fminf(log_keep + before - m, 0.f));
+      scale[at] = expf(fminf(log_in - m, 0.f));
+      floor[at] = expf(-m);
+    }
+    carry = __shfl_sync(0xffffffffu, m, 31);
+  }
+  // the warp of the last range (of the whole portion, if it is one warp's) holds the request's last maximum
+  const bool closes = ranges ? warp == kGateWarps - 1 : true;
+  if (closes && lane == 0 && kept) top_state[(long long)slot * top_stride + h] = carry;
 }
 
 // ---------------------------------------------------------------------------
@@ -958,9 +999,9 @@ extern "C" int einf_memory_gates(const float* gates, int splits, long long split
   if (longest <= 0) longest = num_tokens;
   int shares = (longest + 15) / 16;
   shares = shares < 1 ? 1 : (shares > 128 ? 128 : shares);
-  const dim3 grid(shares + 1, num_requests);      // CTA 0 of a request makes its gates, the others widen its values
+  const dim3 grid(heads + shares, num_requests);  // a CTA per head of a request makes its gates, the others widen its values
   EINF_DISPATCH_2(dtype, T, {
-    return (int)launch_pdl(memory_gates_kernel<T>, grid, dim3(256), 0, stream, gates, splits < 1 ? 1 : splits,
+    return (int)launch_pdl(memory_gates_kernel<T>, grid, dim3(32 * kGateWarps), 0, stream, gates, splits < 1 ? 1 : splits,
                            (size_t)split_stride, bias, cap, (const T*)v, v_stride, top_state, top_stride, num_slots,
                            q_start, state_slots, decay, scale, floor, (T*)v_wide, heads, vdim, columns);
   })

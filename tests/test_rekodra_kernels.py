@@ -188,7 +188,7 @@ def test_combine_with_pass_through_experts_and_a_gated_addend(dev, dtype, tokens
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, dim, vdim, cap", [(2, 48, 48, 15.0), (1, 16, 8, 4.0), (3, 8, 20, 30.0), (4, 64, 64, 15.0),
                                                   (2, 128, 12, 1.0)])
-@pytest.mark.parametrize("portions", [(1, 1, 1), (7, 1, 30, 2), (300,), (130, 129, 1)])
+@pytest.mark.parametrize("portions", [(1, 1, 1), (7, 1, 30, 2), (300,), (130, 129, 1), (1100,), (257, 600)])
 def test_matrix_memory_steps(dev, dtype, heads, dim, vdim, cap, portions):
     """Gates, recurrence on the widened values and output, chained as the mixer chains them, against
     the plain statements; then the same tokens in two steps, which must carry maximum and state."""
