@@ -1359,7 +1359,13 @@ def rekodra_kernels(peak: dict) -> dict:
             mv, mg = proj[:, 2 * keys:2 * keys + m_heads * vdim], proj[:, 2 * keys + m_heads * vdim:]
             decay, scale, floor = (torch.empty(rows, m_heads, device=device) for _ in range(3))
             wide = torch.empty(rows, m_heads * columns, device=device).bfloat16()
-            y = torch.empty(rows, m_heads * columns, device=device)
+            # single tokens of a few requests: several CTAs share a head's rows and leave parts of y
+            parts = 1
+            if max(lengths) == 1:
+                parts = ops.recurrence_step_splits(
+                    requests, m_heads, dim, columns, states[0][:, :m_heads * dim * columns].view(requests, m_heads, dim, columns))
+            y = torch.empty((rows, m_heads * columns) if parts == 1 else (parts, rows, m_heads * columns), device=device)
+            out[f"{name}_memory_recurrence_{what}_parts"] = parts
             weight = torch.ones(m_heads * vdim, device=device)
             mo = torch.empty(rows, m_heads * vdim, device=device).bfloat16()
 

@@ -138,6 +138,8 @@ struct RecurrenceArgs {
   float* state; long long state_stride;
   const int* q_start; const int* state_slots;
   float* y;
+  int y_splits;              // the streaming kernel alone: CTAs that share a head's rows, each leaving its part of y
+  long long y_split_stride;  // floats between two parts of y
   float* segment_state;    // [requests * segments, heads, dim, vdim]: B after the first pass, start states after the walk
   float* segment_decay;    // [requests * segments, heads]
   int num_slots, heads, groups, dim, vdim, act, lanes_per_column, dim_pad, batch, segments, segment_len;
@@ -412,7 +414,10 @@ __global__ void recurrence_walk_kernel(const __grid_constant__ RecurrenceArgs a)
 // thread with 16-byte loads and stores along the rows, S <- a S + k (s v)^T and the thread's part of
 // y = S^T q in the same pass; the row groups' parts of y meet in shared memory.  vdim / 4 is at most
 // the 128 threads (the launcher sends other sizes to the kernel above); where it does not divide
-// them, the threads beyond the last whole row group sit the pass out.
+// them, the threads beyond the last whole row group sit the pass out.  With y_splits > 1 that many
+// CTAs (grid z) share a head's rows, a run of rows each, and leave their parts of y one after the
+// other (y_split_stride floats apart) for the consumer to add up: a few requests with few large
+// heads would otherwise be a few CTAs.
 template <typename T>
 __global__ void __launch_bounds__(kRecurrenceThreads)
 recurrence_step_kernel(const __grid_constant__ RecurrenceArgs a) {
@@ -448,22 +453,24 @@ recurrence_step_kernel(const __grid_constant__ RecurrenceArgs a) {
   const int quads = vdim >> 2;                       // at most 128
   const int cq = threadIdx.x % quads, row0 = threadIdx.x / quads, row_step = kRecurrenceThreads / quads;
   const bool works = row0 < row_step;                // false: a thread beyond the last whole row group
+  const int rows_each = (dim + a.y_splits - 1) / a.y_splits;
+  const int row_begin = (int)blockIdx.z * rows_each, row_end = min(dim, row_begin + rows_each);
   const float4 sv = *reinterpret_cast<const float4*>(vs + 4 * cq);
   float4* state = (slot >= 0 && slot < a.num_slots)
       ? reinterpret_cast<float4*>(a.state + (long long)slot * a.state_stride + ((long long)head * dim) * vdim) + cq : nullptr;
   float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
   constexpr int kInFlight = 8;
-  for (int row = works ? row0 : dim; row < dim; row += row_step * kInFlight) {
+  for (int row = works ? row_begin + row0 : row_end; row < row_end; row += row_step * kInFlight) {
     float4 s[kInFlight];
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {
       const int rr = row + u * row_step;
-      s[u] = (state && rr < dim) ? state[(long long)rr * quads] : make_float4(0.f, 0.f, 0.f, 0.f);
+      s[u] = (state && rr < row_end) ? state[(long long)rr * quads] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {
       const int rr = row + u * row_step;
-      if (rr >= dim) break;
+      if (rr >= row_end) break;
       const float kv = ks[rr], qv = qs[rr];
       s[u].x = fmaf(decay, s[u].x, kv * sv.x);
       s[u].y = fmaf(decay, s[u].y, kv * sv.y);
@@ -478,12 +485,13 @@ recurrence_step_kernel(const __grid_constant__ RecurrenceArgs a) {
   }
   if (works) *reinterpret_cast<float4*>(parts + row0 * vdim + 4 * cq) = y;
   __syncthreads();
-  const float skip = a.skip ? a.skip[head] : 0.f;
+  const float skip = (a.skip && blockIdx.z == 0) ? a.skip[head] : 0.f;      // the skip term once, in the first part
+  float* y_part = a.y + (long long)blockIdx.z * a.y_split_stride;
   for (int c = threadIdx.x; c < vdim; c += kRecurrenceThreads) {
     float total = 0.f;
     for (int g = 0; g < row_step; ++g) total += parts[g * vdim + c];
     const float v = to_float(vg[c]);
-    a.y[((long long)t * a.heads + head) * vdim + c] = total + skip * (act ? silu_f(v) : v);
+    y_part[((long long)t * a.heads + head) * vdim + c] = total + skip * (act ? silu_f(v) : v);
   }
 }
 
@@ -682,11 +690,12 @@ memory_gates_kernel(const float* __restrict__ gates, int splits, size_t split_st
 //   out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate)
 // head by head, in 32-bit.  One warp per (token, head).
 // ---------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool kParts>
 __global__ void memory_output_kernel(const float* __restrict__ y, const float* __restrict__ floor,
                                      const T* __restrict__ gate, long long gate_stride,
                                      const float* __restrict__ weight, T* __restrict__ out, long long pairs, int heads,
-                                     int vdim, int columns, float query_scale, float eps, float denominator_eps) {
+                                     int vdim, int columns, float query_scale, float eps, float denominator_eps,
+                                     int y_splits, long long y_split_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -695,11 +704,23 @@ __global__ void memory_output_kernel(const float* __restrict__ y, const float* _
   const long long t = pair / heads;
   const int h = (int)(pair - t * heads);
   const float* row = y + (t * heads + h) * columns;
-  const float below = fmaxf(fabsf(query_scale * row[vdim]), floor[pair]) + denominator_eps;
+  // y may come as the parts of several CTAs that shared the head's rows: added up here, in order
+  auto value = [&](int d) {
+    if (!kParts) return row[d];
+    // up to eight parts, all their loads in flight together, added in order (the launcher checks the count)
+    float part[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) part[s] = s < y_splits ? row[(long long)s * y_split_stride + d] : 0.f;
+    float total = 0.f;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) total += part[s];
+    return total;
+  };
+  const float below = fmaxf(fabsf(query_scale * value(vdim)), floor[pair]) + denominator_eps;
   const float factor = query_scale / below;
   float ss = 0.f;
   for (int d = lane; d < vdim; d += 32) {
-    const float o = row[d] * factor;
+    const float o = value(d) * factor;
     ss += o * o;
   }
   const float unit = rsqrtf(warp_sum(ss) / (float)vdim + eps);
@@ -707,7 +728,7 @@ __global__ void memory_output_kernel(const float* __restrict__ y, const float* _
   T* o_row = out + (t * heads + h) * vdim;
   for (int d = lane; d < vdim; d += 32) {
     const float g = to_float(g_row[d]);
-    o_row[d] = from_float<T>(row[d] * factor * unit * weight[h * vdim + d] * (1.f / (1.f + expf(-g))));
+    o_row[d] = from_float<T>(value(d) * factor * unit * weight[h * vdim + d] * (1.f / (1.f + expf(-g))));
   }
 }
 
@@ -867,9 +888,10 @@ extern "C" int einf_linear_recurrence(const void* q, const void* k, const void* 
                                       float* state, long long state_stride, int num_slots, const int* q_start,
                                       const int* state_slots, int num_requests, float* y, int heads, int groups,
                                       int dim, int vdim, int act, int rows, int columns, int segments,
-                                      int segment_len, float* segment_state, float* segment_decay,
-                                      cudaStream_t stream) {
+                                      int segment_len, float* segment_state, float* segment_decay, int y_splits,
+                                      long long y_split_stride, cudaStream_t stream) {
   if (num_requests == 0) return 0;
+  if (y_splits < 1 || y_splits > 64) return (int)cudaErrorInvalidValue;
   if (heads <= 0 || groups <= 0 || heads % groups || dim <= 0 || vdim <= 0 || dim > 512 || heads > 65535 ||
       segments < 1 || segment_len < 1 || (long long)num_requests * segments > 65535 ||
       (segments > 1 && (!segment_state || !segment_decay)))
@@ -886,6 +908,7 @@ extern "C" int einf_linear_recurrence(const void* q, const void* k, const void* 
   a.state = state; a.state_stride = state_stride;
   a.q_start = q_start; a.state_slots = state_slots;
   a.y = y;
+  a.y_splits = y_splits; a.y_split_stride = y_split_stride;
   a.segment_state = segment_state; a.segment_decay = segment_decay;
   a.num_slots = num_slots; a.heads = heads; a.groups = groups; a.dim = dim; a.vdim = vdim; a.act = act;
   a.segments = segments; a.segment_len = segment_len;
@@ -895,11 +918,12 @@ extern "C" int einf_linear_recurrence(const void* q, const void* k, const void* 
     a.lanes_per_column = 0; a.dim_pad = dim; a.batch = 1;
     const int row_groups = kRecurrenceThreads / (vdim / 4);
     const size_t bytes = (size_t)(2 * dim + vdim + row_groups * vdim) * sizeof(float);
-    const dim3 step_grid(heads, num_requests);
+    const dim3 step_grid(heads, num_requests, y_splits);
     EINF_DISPATCH_2(dtype, T, {
       return (int)launch_pdl(recurrence_step_kernel<T>, step_grid, kRecurrenceThreads, bytes, stream, a);
     })
   }
+  if (y_splits != 1) return (int)cudaErrorInvalidValue;      // parts of y are the streaming kernel's alone
   int lanes = 1;
   while (lanes * rows < dim) lanes <<= 1;
   a.lanes_per_column = lanes;
@@ -1009,16 +1033,21 @@ extern "C" int einf_memory_gates(const float* gates, int splits, long long split
 
 extern "C" int einf_memory_output(const float* y, const float* floor, const void* gate, int dtype, long long gate_stride,
                                   const float* weight, void* out, int num_tokens, int heads, int vdim, int columns,
-                                  float query_scale, float eps, float denominator_eps, cudaStream_t stream) {
+                                  float query_scale, float eps, float denominator_eps, int y_splits,
+                                  long long y_split_stride, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
-  if (heads <= 0 || vdim <= 0 || columns <= vdim) return (int)cudaErrorInvalidValue;
+  if (heads <= 0 || vdim <= 0 || columns <= vdim || y_splits < 1 || y_splits > 8) return (int)cudaErrorInvalidValue;
   const long long pairs = (long long)num_tokens * heads;
   const int threads = 128;
   const long long blocks = (pairs * 32 + threads - 1) / threads;
   if (blocks >= (1ll << 31)) return (int)cudaErrorInvalidValue;
   EINF_DISPATCH_2(dtype, T, {
-    return (int)launch_pdl(memory_output_kernel<T>, (int)blocks, threads, 0, stream, y, floor, (const T*)gate,
+    if (y_splits == 1)
+      return (int)launch_pdl(memory_output_kernel<T, false>, (int)blocks, threads, 0, stream, y, floor, (const T*)gate,
+                             gate_stride, weight, (T*)out, pairs, heads, vdim, columns, query_scale, eps,
+                             denominator_eps, y_splits, y_split_stride);
+    return (int)launch_pdl(memory_output_kernel<T, true>, (int)blocks, threads, 0, stream, y, floor, (const T*)gate,
                            gate_stride, weight, (T*)out, pairs, heads, vdim, columns, query_scale, eps,
-                           denominator_eps);
+                           denominator_eps, y_splits, y_split_stride);
   })
 }

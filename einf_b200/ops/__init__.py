@@ -1186,6 +1186,22 @@ def recurrence_plan(num_requests: int, max_q_len: Optional[int], heads: int, dim
     return -(-max_q_len // segment_len), segment_len
 
 
+#: most CTAs that share one head's rows in a step of single tokens
+RECURRENCE_STEP_MAX_SPLITS = 8
+
+
+def recurrence_step_splits(num_requests: int, heads: int, dim: int, vdim: int, state: torch.Tensor) -> int:
+    """How many CTAs share a head's rows when :func:`linear_recurrence` runs a step of single tokens:
+    1 unless the requests and heads alone leave most multiprocessors without a CTA and the streaming
+    kernel takes the sizes; then enough for about two CTAs a multiprocessor, at least 16 rows each.
+    ``y`` is then ``[splits, tokens, heads * vdim]`` and its consumer adds the parts up."""
+    if vdim % 4 or vdim // 4 > 128 or state.stride(0) % 4 or state.data_ptr() % 16:
+        return 1
+    ctas = max(1, num_requests * heads)
+    wanted = (2 * _sm_count()) // ctas
+    return max(1, min(RECURRENCE_STEP_MAX_SPLITS, wanted, dim // 16))
+
+
 def linear_recurrence(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -1218,7 +1234,9 @@ def linear_recurrence(
     heads]`` or 1; ``skip [heads]`` or 0; all float32.  ``silu_inputs``: q, k and v pass SiLU as
     they are read.  ``state [slots, heads, dim, vdim]`` float32 (slot stride may be larger) is read
     at the start of each request's portion and written at its end; ``y [tokens, heads * vdim]``
-    float32.  ``max_q_len`` is the longest portion of the step as the host knows it (None: unknown,
+    float32, or, in a step of single tokens (``max_q_len`` 1), ``[splits, tokens, heads * vdim]`` with
+    ``splits`` from :func:`recurrence_step_splits`: the parts of that many CTAs per head, for the
+    consumer to add up.  ``max_q_len`` is the longest portion of the step as the host knows it (None: unknown,
     no portion is cut into segments); ``rows`` (0, 4, 8, 16), ``columns`` (0, 1, 2) and ``segment_len``
     override the launch's own choices (:func:`recurrence_plan`), for tests and measurements."""
     tokens = v.shape[0]
@@ -1233,7 +1251,12 @@ def linear_recurrence(
     if state.dtype != torch.float32 or state.shape[1:] != (heads, dim, vdim) or \
             state[0].stride() != (dim * vdim, vdim, 1):
         raise ValueError(f"state must be float32 [slots, {heads}, {dim}, {vdim}] with contiguous slots")
-    if y.dtype != torch.float32 or y.shape != (tokens, heads * vdim) or not y.is_contiguous():
+    y_splits = 1
+    if y.dim() == 3:
+        y_splits = y.shape[0]
+        if max_q_len != 1 or y_splits != recurrence_step_splits(state_slots.shape[0], heads, dim, vdim, state):
+            raise ValueError("y in parts is for a step of single tokens, with splits from recurrence_step_splits")
+    if y.dtype != torch.float32 or y.shape[-2:] != (tokens, heads * vdim) or not y.is_contiguous():
         raise ValueError(f"y must be contiguous float32 {(tokens, heads * vdim)}")
     if (head_decay is None) == (token_decay is None):
         raise ValueError("give head_decay or token_decay")
@@ -1259,7 +1282,7 @@ def linear_recurrence(
         "einf_linear_recurrence",
         [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
          c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-         c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+         c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_longlong, c_void_p],
     )
     _check(
         fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), _code(q), _rows_of(q, "q"), _rows_of(k, "k"), _rows_of(v, "v"),
@@ -1269,7 +1292,7 @@ def linear_recurrence(
            _opt(state_slots, "state_slots", torch.int32), requests, _dev(y, "y"), heads, groups, dim,
            vdim, 1 if silu_inputs else 0, int(rows), int(columns), segments, segment_len,
            _opt(segment_state, "segment_state", torch.float32), _opt(segment_decay, "segment_decay", torch.float32),
-           _stream()),
+           y_splits, tokens * heads * vdim, _stream()),
         "linear_recurrence",
     )
     if segments > 1:
@@ -1402,11 +1425,13 @@ def memory_output(
         out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate)
 
     head by head; ``floor`` float32 ``[tokens, heads]``, ``weight`` float32 ``[heads * vdim]``, ``gate`` and
-    ``out`` ``[tokens, heads * vdim]`` of one dtype (``gate`` may be columns of a wider matrix)."""
-    tokens = y.shape[0]
-    columns = y.shape[1] // max(heads, 1)
-    if y.dtype != torch.float32 or not y.is_contiguous() or y.shape != (tokens, heads * columns) or columns <= vdim:
-        raise ValueError("y must be contiguous float32 [tokens, heads * columns] with columns > vdim")
+    ``out`` ``[tokens, heads * vdim]`` of one dtype (``gate`` may be columns of a wider matrix).  ``y`` may be
+    the stacked parts ``[splits, tokens, heads * columns]`` that a step of single tokens leaves: added up here."""
+    tokens = y.shape[-2]
+    columns = y.shape[-1] // max(heads, 1)
+    y_splits = y.shape[0] if y.dim() == 3 else 1
+    if y.dtype != torch.float32 or not y.is_contiguous() or y.shape[-2:] != (tokens, heads * columns) or columns <= vdim:
+        raise ValueError("y must be contiguous float32 [tokens, heads * columns] (or parts of it, stacked) with columns > vdim")
     if floor.dtype != torch.float32 or floor.shape != (tokens, heads) or not floor.is_contiguous():
         raise ValueError(f"floor must be contiguous float32 {(tokens, heads)}")
     if gate.shape != (tokens, heads * vdim) or out.shape != gate.shape or gate.dtype != out.dtype:
@@ -1420,12 +1445,12 @@ def memory_output(
     fn = _fn(
         "einf_memory_output",
         [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
-         c_float, c_float, c_void_p],
+         c_float, c_float, c_int, c_longlong, c_void_p],
     )
     _check(
         fn(_dev(y, "y"), _dev(floor, "floor"), gate.data_ptr(), _code(gate), _rows_of(gate, "gate"),
            _dev(weight, "weight"), _dev(out, "out"), tokens, heads, vdim, columns, float(query_scale), float(eps),
-           float(denominator_eps), _stream()),
+           float(denominator_eps), y_splits, tokens * heads * columns, _stream()),
         "memory_output",
     )
 

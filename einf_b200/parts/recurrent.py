@@ -359,7 +359,12 @@ class MatrixMemory(_RecurrentMixer):
         v_wide = torch.empty((tokens, heads * self.columns), dtype=proj.dtype, device=device)
         ops.memory_gates(raw_gates, self.gate_bias, self.gate_cap, v, top, ctx.q_start, ctx.state_slots, decay, scale,
                          floor, v_wide, heads, self.vdim, max_q_len=ctx.max_q_len)
-        y = torch.empty((tokens, heads * self.columns), dtype=torch.float32, device=device)
+        # a step of single tokens with few requests: several CTAs share a head's rows and leave parts of y
+        parts = 1
+        if ctx.max_q_len == 1:
+            parts = ops.recurrence_step_splits(ctx.num_requests, heads, self.dim, self.columns, memory)
+        shape = (tokens, heads * self.columns) if parts == 1 else (parts, tokens, heads * self.columns)
+        y = torch.empty(shape, dtype=torch.float32, device=device)
         ops.linear_recurrence(
             q, k, v_wide, memory, ctx.q_start, ctx.state_slots, y, heads, heads, self.dim, self.columns,
             token_decay=decay, token_scale=scale, max_q_len=ctx.max_q_len,

@@ -366,6 +366,9 @@ def linear_recurrence(q, k, v, state, q_start, state_slots, y, heads, groups, di
         return t / (1 + torch.exp(-t)) if silu_inputs else t
 
     tokens = v.shape[0]
+    if y.dim() == 3:            # parts of several CTAs: everything in the first, zeros in the others
+        y.zero_()
+        y = y[0]
     qf, kf = act(q).reshape(tokens, groups, dim), act(k).reshape(tokens, groups, dim)
     vf = act(v).reshape(tokens, heads, vdim)
     per_group = heads // groups
@@ -404,6 +407,10 @@ def memory_value_columns(vdim):
     return (vdim + 1 + 3) // 4 * 4
 
 
+def recurrence_step_splits(num_requests, heads, dim, vdim, state):
+    return 1
+
+
 def memory_gates(gates, bias, cap, v, top_state, q_start, state_slots, decay, scale, floor, v_wide, heads, vdim,
                  max_q_len=None):
     z = _summed(gates) + bias
@@ -430,6 +437,7 @@ def memory_gates(gates, bias, cap, v, top_state, q_start, state_slots, decay, sc
 
 
 def memory_output(y, floor, gate, weight, out, heads, vdim, query_scale, eps, denominator_eps):
+    y = _summed(y)
     tokens = y.shape[0]
     wide = y.reshape(tokens, heads, -1)
     below = torch.maximum((query_scale * wide[:, :, vdim]).abs(), floor) + denominator_eps
@@ -641,7 +649,7 @@ _NAMES = (
     "gated_norm", "recurrence_plan", "latent_down_store", "latent_q_store", "per_head_project", "router_topk",
     "moe_dispatch", "moe_gemm", "moe_combine", "softcap", "latent_decode_attention", "latent_decode_splits", "moe_gemm_on_tensor_cores", "moe_gemm_splits",
     "act_mul", "norm_conv", "stream_tail", "paged_attention_mixed", "gated_scan", "memory_gates", "memory_output",
-    "norm_join", "memory_value_columns",
+    "norm_join", "memory_value_columns", "recurrence_step_splits",
 )
 
 

@@ -220,7 +220,9 @@ def test_matrix_memory_steps(dev, dtype, heads, dim, vdim, cap, portions):
         top = state[:, heads * dim * columns:]
         module.memory_gates(raw[first:last], bias, cap, v[first:last], top, starts, step_slots, decay, scale, floor, wide,
                             heads, vdim)
-        y = torch.empty((n, heads * columns), dtype=torch.float32, device=dev)
+        # single tokens of a few requests: the kernel's CTAs share a head's rows and leave parts of y
+        parts = module.recurrence_step_splits(step_slots.shape[0], heads, dim, columns, memory) if longest == 1 else 1
+        y = torch.empty((n, heads * columns) if parts == 1 else (parts, n, heads * columns), dtype=torch.float32, device=dev)
         module.linear_recurrence(q[first:last], k[first:last], wide, memory, starts, step_slots, y, heads, heads, dim,
                                  columns, token_decay=decay, token_scale=scale, max_q_len=longest)
         out = torch.empty((n, heads * vdim), dtype=dtype, device=dev)
